@@ -47,6 +47,7 @@ class PagedKVNeed:
                                               # "attention": csrc/attention.cu, whose decode launches the step plans kv splits for
     even_cut: bool = True            # whether a decode step may deal this cache's keys out evenly over the blocks
     shared_kv: bool = False          # the values are read out of the key rows: one array is kept, not two
+    v_head_dim: Optional[int] = None # size of a value row where it differs from a key row's (None: head_dim)
 
 
 @dataclasses.dataclass(frozen=True)

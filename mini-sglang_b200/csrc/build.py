@@ -136,6 +136,7 @@ def load_library(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
 COMMON_SOURCES = ["elementwise.cu", "sampling.cu", "gemm_small_m.cu", "gemm_tc.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
 MIXER_SOURCES = ["mixers.cu"]
+GATED_MIXER_SOURCES = ["mixers_gated.cu"]
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))   # head sizes the tensor-core attention kernel is built for
 
 
@@ -151,6 +152,12 @@ def mixers_library() -> ctypes.CDLL:
     """The kernels of csrc/mixers.cu (norms, convolutions, windowed and linear attention, gated activations); built only
     for models that have such parts."""
     return load_library("mixers", MIXER_SOURCES)
+
+
+def gated_mixers_library() -> ctypes.CDLL:
+    """The kernels of csrc/mixers_gated.cu (sigmoid attention, gated recurrences, state-space scan, routed experts); built
+    only for models that have such parts."""
+    return load_library("mixers_gated", GATED_MIXER_SOURCES)
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
@@ -182,7 +189,8 @@ def decode_step_library(head_dim: int) -> ctypes.CDLL:
 
 def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
     """Compile every library ahead of time (used by the repository's build check)."""
-    paths = [compile_library("common", COMMON_SOURCES), compile_library("mixers", MIXER_SOURCES)]
+    paths = [compile_library("common", COMMON_SOURCES), compile_library("mixers", MIXER_SOURCES),
+             compile_library("mixers_gated", GATED_MIXER_SOURCES)]
     for hd in head_dims:
         paths.append(compile_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd}))
     paths.append(compile_library("attention_noalloc_d128", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": 128}))

@@ -1,0 +1,911 @@
+// Kernels of mixers and feed-forwards whose weights over the past are gates rather than a softmax, and of routed experts
+// (sm_100a; plain C entry points, loaded by ops.py as the library "mixers_gated", built only for models with such parts):
+//
+//   embed_positions_kernel     float(E[id]) * c + float(P[position]): opens the float32 stream of a model with learned places
+//   headnorm_kvwrite_kernel    per-head RMS norm of q and k (one weight for all heads), q warmed up by its place, K and V rows
+//                              (of head sizes of their own) into the paged cache
+//   sigmoid_attention_kernel   causal attention whose weight of a key is sigmoid(q.k * scale + bias[head][distance]): no sum
+//                              over keys divides anything, so pieces of the keys simply add up (sum_pieces_kernel)
+//   mingru_kernel              S_t = (1 - z_t) S_(t-1) + z_t c_t per channel with gates from the current token, times silu(g)
+//   pair_norm_kernel           c * (rms(a) * wa + rms(b) * wb) in float32: two mixers' outputs joined
+//   causal_conv_act_kernel     short causal convolution per channel with bias and silu, continued from a request's last inputs;
+//                              conv_state_shift_kernel brings those up to date
+//   ssm_scan_kernel            S_t = exp(-exp(A) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t per head, token by token
+//   gate_group_norm_kernel     (y * silu(z)) RMS-normed in equal parts of the row, times a weight
+//   unary_act_kernel           relu(x)^2 (and the other activations), times a constant
+//   route_kernel               router logits in float32, sigmoid scores, correction, limitation to the best groups, the top
+//                              experts and their weights: one block per token
+//   expert_gate_up_kernel, expert_down_kernel      the chosen experts' products for a few tokens, straight from the experts'
+//                              stacked weights (weight-streaming, one warp per output row)
+//   expert_count_kernel, expert_place_kernel, expert_gather_kernel, expert_combine_kernel    many tokens: the (token, choice)
+//                              pairs in the order of their experts (stable), rows gathered for one product per expert, and the
+//                              weighted sum of every token's rows
+//
+// Scores, weights, norms, gates, decays, states and everything that enters a recurrence are float32; T is the type of the
+// activations between kernels (float or bfloat16).  The order of every sum at a position is fixed by absolute positions, never
+// by how the tokens were cut into steps or by what else is in the batch.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float gelu_tanhf_(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// ln(1 + e^x) without a threshold: max(x, 0) + ln(1 + e^-|x|)
+__device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Embedding with a learned vector per place
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_positions_kernel(const int* __restrict__ ids, const int* __restrict__ positions, const T* __restrict__ table,
+                                       const T* __restrict__ places, float* __restrict__ out, int H, int V, int n_places, float c) {
+    const int t = blockIdx.x;
+    const int id = min(max(ids[t], 0), V - 1), pos = min(max(positions[t], 0), n_places - 1);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t)t * H + i] = to_f32<T>(table[(size_t)id * H + i]) * c + to_f32<T>(places[(size_t)pos * H + i]);
+}
+
+MSGL_API int msgl_embed_positions(const int* ids, const int* positions, const void* table, const void* places, float* out, int T_,
+                                  int H, int V, int n_places, float c, int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (H <= 0 || V <= 0 || n_places <= 0) return MSGL_ERR_SIZE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == MSGL_F32)
+        embed_positions_kernel<float><<<T_, threads, 0, stream>>>(ids, positions, (const float*)table, (const float*)places, out, H, V, n_places, c);
+    else if (dtype == MSGL_BF16)
+        embed_positions_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(ids, positions, (const __nv_bfloat16*)table,
+                                                                          (const __nv_bfloat16*)places, out, H, V, n_places, c);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Per-head RMS norm of q and k, q times a factor that grows with the place, K and V into the paged cache
+//
+//   proj row: q at q_off (n_q * d), k at k_off (n_kv * d), v at v_off (n_kv * dv)
+//   q_out[t, h, :] = q / sqrt(mean(q^2) + eps) * wq * (1 + coef * ln(floor((pos + 1) / every) + 1))
+//   K cache [page][kv head][slot][d] <- k / sqrt(mean(k^2) + eps) * wk;  V cache [page][kv head][slot][dv] <- v
+// One warp per (token, job), jobs = the q heads, then the k heads, then the v heads.
+// ---------------------------------------------------------------------------------------
+struct HeadNormParams {
+    const void* proj; long long stride; int q_off, k_off, v_off;
+    int n_q, n_kv, d, dv;
+    const float* wq; const float* wk; float eps;
+    float temp_coef; int temp_every;
+    const int* positions; const int* out_loc;
+    void* q_out; void* k_cache; void* v_cache; int page_size; int T;
+};
+
+template <typename T>
+__global__ void headnorm_kvwrite_kernel(const HeadNormParams p) {
+    const int jobs = p.n_q + 2 * p.n_kv;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)p.T * jobs) return;
+    const int t = (int)(w / jobs), job = (int)(w - (long long)t * jobs);
+    const T* row = reinterpret_cast<const T*>(p.proj) + (size_t)t * p.stride;
+    if (job < p.n_q) {
+        const T* src = row + p.q_off + (size_t)job * p.d;
+        float ss = 0.f;
+        for (int e = lane; e < p.d; e += 32) { const float v = to_f32<T>(src[e]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        float f = rsqrtf(ss / (float)p.d + p.eps);
+        if (p.temp_coef != 0.f) {
+            const int pos = p.positions[t];
+            f *= 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f);
+        }
+        T* dst = reinterpret_cast<T*>(p.q_out) + ((size_t)t * p.n_q + job) * p.d;
+        for (int e = lane; e < p.d; e += 32) dst[e] = from_f32<T>(to_f32<T>(src[e]) * f * p.wq[e]);
+        return;
+    }
+    if (p.out_loc == nullptr) return;
+    const int loc = p.out_loc[t];
+    const int page = loc / p.page_size, off = loc - page * p.page_size;
+    if (job < p.n_q + p.n_kv) {
+        const int g = job - p.n_q;
+        const T* src = row + p.k_off + (size_t)g * p.d;
+        float ss = 0.f;
+        for (int e = lane; e < p.d; e += 32) { const float v = to_f32<T>(src[e]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float f = rsqrtf(ss / (float)p.d + p.eps);
+        T* dst = reinterpret_cast<T*>(p.k_cache) + (((size_t)page * p.n_kv + g) * p.page_size + off) * p.d;
+        for (int e = lane; e < p.d; e += 32) dst[e] = from_f32<T>(to_f32<T>(src[e]) * f * p.wk[e]);
+    } else {
+        const int g = job - p.n_q - p.n_kv;
+        const T* src = row + p.v_off + (size_t)g * p.dv;
+        T* dst = reinterpret_cast<T*>(p.v_cache) + (((size_t)page * p.n_kv + g) * p.page_size + off) * p.dv;
+        for (int e = lane; e < p.dv; e += 32) dst[e] = src[e];
+    }
+}
+
+MSGL_API int msgl_headnorm_kvwrite(const void* proj, long long stride, int q_off, int k_off, int v_off, int n_q, int n_kv, int d, int dv,
+                                   const float* wq, const float* wk, float eps, float temp_coef, int temp_every, const int* positions,
+                                   const int* out_loc, void* q_out, void* k_cache, void* v_cache, int page_size, int T_, int dtype,
+                                   cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (n_q <= 0 || n_kv <= 0 || d <= 0 || dv <= 0 || page_size < 1 || (temp_coef != 0.f && temp_every < 1)) return MSGL_ERR_SIZE;
+    HeadNormParams p;
+    p.proj = proj; p.stride = stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.dv = dv;
+    p.wq = wq; p.wk = wk; p.eps = eps; p.temp_coef = temp_coef; p.temp_every = temp_every; p.positions = positions; p.out_loc = out_loc;
+    p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache; p.page_size = page_size; p.T = T_;
+    const long long warps = (long long)T_ * (n_q + 2 * n_kv);
+    const int per_block = 8;
+    const unsigned grid = (unsigned)((warps + per_block - 1) / per_block);
+    if (dtype == MSGL_F32) headnorm_kvwrite_kernel<float><<<grid, per_block * 32, 0, stream>>>(p);
+    else if (dtype == MSGL_BF16) headnorm_kvwrite_kernel<__nv_bfloat16><<<grid, per_block * 32, 0, stream>>>(p);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Causal attention with sigmoid weights over the paged cache
+//
+//   o[i, h, :] = sum_{j <= i} sigmoid(q[i, h] . k[j, g] * scale + bias[h][min(i - j, L - 1)]) * v[j, g, :]
+//
+// A block owns a tile of QT tokens x GH query heads of one kv head (SA_ROWS rows, one warp each) and walks the keys in
+// chunks of 32 anchored at multiples of 32.  In the score phase lane l of a row's warp takes key l of the chunk, in the value
+// phase lane l takes the output elements l, l + 32, ...  With `splits` > 1 (steps in which every request brings one token)
+// block z walks the keys [z * split_keys, (z + 1) * split_keys) only and leaves its sums in `part`; the pieces are added in
+// order by sum_pieces_kernel.
+// ---------------------------------------------------------------------------------------
+#define SA_ROWS 8
+#define SA_KC 32
+#define SA_MAX_DPL 16       // value head sizes up to 512
+
+struct SigmoidAttnParams {
+    const void* q;            // [T, n_q, d]
+    const void* k_cache; const void* v_cache;
+    const int* q_start; const int* kv_len; const int* block_table; int bt_stride;
+    int uniform;                                  // every request brings one token: block x takes request x
+    const float* bias; int bias_len;              // [n_q][bias_len]
+    void* out; long long out_stride;              // [T rows][n_q * dv]
+    float* part; int splits, split_keys;          // [splits][T][n_q][dv] float32
+    int T, B, n_q, n_kv, d, dv, page_size, QT, GH;
+    float scale;
+};
+
+template <typename T, int DPL /* output elements per lane: value head sizes up to 32 * DPL */>
+__global__ void __launch_bounds__(SA_ROWS * 32) sigmoid_attention_kernel(const SigmoidAttnParams p) {
+    extern __shared__ float smem[];
+    const int d = p.d, dv = p.dv;
+    float* qs = smem;                                // [SA_ROWS][d]
+    float* ks = qs + SA_ROWS * d;                    // [SA_KC][d + 1]
+    float* vs = ks + SA_KC * (d + 1);                // [SA_KC][dv]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ int tile_sh[2];
+    int req, t0;
+    if (p.uniform) {
+        req = blockIdx.x; t0 = 0;
+    } else {
+        if (tid == 0) {
+            int left = blockIdx.x, found = -1, at = 0;
+            for (int r = 0; r < p.B; ++r) {
+                const int nt = (p.q_start[r + 1] - p.q_start[r] + p.QT - 1) / p.QT;
+                if (left < nt) { found = r; at = left * p.QT; break; }
+                left -= nt;
+            }
+            tile_sh[0] = found; tile_sh[1] = at;
+        }
+        __syncthreads();
+        req = tile_sh[0]; t0 = tile_sh[1];
+    }
+    if (req < 0 || req >= p.B) return;
+    const int G = p.n_q / p.n_kv;
+    const int n_chunks = (G + p.GH - 1) / p.GH;
+    const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
+    const int q_base = p.q_start[req], q_len = p.q_start[req + 1] - q_base, kv_len = p.kv_len[req];
+    const int n_tok = min(p.QT, q_len - t0);
+    if (n_tok <= 0) return;
+    const int p_min = kv_len - q_len + t0, p_max = p_min + n_tok - 1;
+    int key_lo = 0, key_hi = p_max + 1;              // keys this block walks: [key_lo, key_hi)
+    if (p.splits > 1) {
+        key_lo = blockIdx.z * p.split_keys;
+        key_hi = min(key_hi, key_lo + p.split_keys);
+    }
+
+    const int tl = warp / p.GH, hl = warp - tl * p.GH;
+    const int hg = chunk * p.GH + hl;
+    const bool row_ok = tl < n_tok && hg < G && tl < p.QT;
+    const int head = kvh * G + (row_ok ? hg : 0);
+    const int tok = q_base + t0 + (row_ok ? tl : 0);
+    const int pos = p_min + tl;
+    const T* qg = reinterpret_cast<const T*>(p.q);
+    for (int e = lane; e < d; e += 32) qs[warp * d + e] = row_ok ? to_f32<T>(qg[((size_t)tok * p.n_q + head) * d + e]) : 0.f;
+    const float* bias = p.bias + (size_t)head * p.bias_len;
+    const T* kc = reinterpret_cast<const T*>(p.k_cache);
+    const T* vc = reinterpret_cast<const T*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)req * p.bt_stride;
+
+    float o[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+
+    for (int key0 = key_lo - key_lo % SA_KC; key0 < key_hi; key0 += SA_KC) {
+        __syncthreads();
+        for (int idx = tid; idx < SA_KC * d; idx += SA_ROWS * 32) {
+            const int kr = idx / d, e = idx - kr * d;
+            const int key = key0 + kr;
+            float kv = 0.f;
+            if (key >= key_lo && key < key_hi) {
+                const int page = bt[key / p.page_size];
+                kv = to_f32<T>(kc[(((size_t)page * p.n_kv + kvh) * p.page_size + (key % p.page_size)) * d + e]);
+            }
+            ks[kr * (d + 1) + e] = kv;
+        }
+        for (int idx = tid; idx < SA_KC * dv; idx += SA_ROWS * 32) {
+            const int kr = idx / dv, e = idx - kr * dv;
+            const int key = key0 + kr;
+            float vv = 0.f;
+            if (key >= key_lo && key < key_hi) {
+                const int page = bt[key / p.page_size];
+                vv = to_f32<T>(vc[(((size_t)page * p.n_kv + kvh) * p.page_size + (key % p.page_size)) * dv + e]);
+            }
+            vs[kr * dv + e] = vv;
+        }
+        __syncthreads();
+        const int key = key0 + lane;
+        const bool vis = row_ok && key <= pos && key >= key_lo && key < key_hi;
+        float pr = 0.f;
+        if (vis) {
+            float acc = 0.f;
+            const float* qr = qs + warp * d;
+            const float* kr = ks + lane * (d + 1);
+            for (int e = 0; e < d; ++e) acc = fmaf(qr[e], kr[e], acc);
+            pr = sigmoidf_(acc * p.scale + bias[min(pos - key, p.bias_len - 1)]);
+        }
+        if (__ballot_sync(0xffffffffu, vis) == 0u) continue;        // warp-uniform
+        for (int j = 0; j < SA_KC; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            if (pj == 0.f) continue;                                 // warp-uniform
+            const float* vr = vs + j * dv;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int e = lane + 32 * i;
+                if (e < dv) o[i] = fmaf(pj, vr[e], o[i]);
+            }
+        }
+    }
+    if (!row_ok) return;
+    if (p.splits > 1) {
+        float* pg = p.part + (((size_t)blockIdx.z * p.T + tok) * p.n_q + head) * dv;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int e = lane + 32 * i;
+            if (e < dv) pg[e] = o[i];
+        }
+        return;
+    }
+    T* og = reinterpret_cast<T*>(p.out) + (size_t)tok * p.out_stride + (size_t)head * dv;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < dv) og[e] = from_f32<T>(o[i]);
+    }
+}
+
+// out[t, c] = sum over the pieces s, in order, of part[s][t][c]; only the pieces that hold keys of the token's request
+template <typename T>
+__global__ void sum_pieces_kernel(const float* __restrict__ part, const int* __restrict__ kv_len, const int* __restrict__ token_req,
+                                  T* __restrict__ out, long long out_stride, int T_, int N, int splits, int split_keys) {
+    const int t = blockIdx.x;
+    const int r = token_req ? token_req[t] : t;
+    const int used = min(splits, (kv_len[r] + split_keys - 1) / split_keys);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < used; ++s) acc += part[((size_t)s * T_ + t) * N + c];
+        out[(size_t)t * out_stride + c] = from_f32<T>(acc);
+    }
+}
+
+MSGL_API int msgl_sigmoid_attention(const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
+                                    const int* block_table, int bt_stride, int uniform, int n_tiles, const float* bias, int bias_len,
+                                    void* out, long long out_stride, float* part, int splits, int split_keys, int T_, int B, int n_q,
+                                    int n_kv, int d, int dv, int page_size, int QT, int GH, float scale, int dtype, cudaStream_t stream) {
+    if (n_tiles <= 0) return MSGL_OK;
+    if (d <= 0 || dv <= 0 || dv > 32 * SA_MAX_DPL || d > 32 * SA_MAX_DPL || n_kv <= 0 || n_q % n_kv || QT < 1 || GH < 1 ||
+        QT * GH > SA_ROWS || page_size < 1 || bias == nullptr || bias_len < 1 || splits < 1 ||
+        (splits > 1 && (!uniform || part == nullptr || split_keys < SA_KC || split_keys % SA_KC)))
+        return MSGL_ERR_SIZE;
+    SigmoidAttnParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
+    p.bt_stride = bt_stride; p.uniform = uniform; p.bias = bias; p.bias_len = bias_len; p.out = out; p.out_stride = out_stride;
+    p.part = part; p.splits = splits; p.split_keys = split_keys; p.T = T_; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.dv = dv;
+    p.page_size = page_size; p.QT = QT; p.GH = GH; p.scale = scale;
+    const int G = n_q / n_kv;
+    const dim3 grid(n_tiles, n_kv * ((G + GH - 1) / GH), splits);
+    const size_t smem = ((size_t)SA_ROWS * d + (size_t)SA_KC * (d + 1) + (size_t)SA_KC * dv) * sizeof(float);
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int dpl = (dv + 31) / 32;
+#define SA_LAUNCH(N)                                                                                                         \
+    do {                                                                                                                     \
+        static MsglOncePerDevice once;                                                                                       \
+        if (smem > 48 * 1024 && once.due()) {                                                                                \
+            cudaFuncSetAttribute(sigmoid_attention_kernel<float, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            cudaFuncSetAttribute(sigmoid_attention_kernel<__nv_bfloat16, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            once.mark();                                                                                                     \
+        }                                                                                                                    \
+        if (dtype == MSGL_F32) sigmoid_attention_kernel<float, N><<<grid, SA_ROWS * 32, smem, stream>>>(p);                  \
+        else sigmoid_attention_kernel<__nv_bfloat16, N><<<grid, SA_ROWS * 32, smem, stream>>>(p);                            \
+    } while (0)
+    if (dpl <= 1) SA_LAUNCH(1);
+    else if (dpl <= 2) SA_LAUNCH(2);
+    else if (dpl <= 3) SA_LAUNCH(3);
+    else if (dpl <= 4) SA_LAUNCH(4);
+    else if (dpl <= 8) SA_LAUNCH(8);
+    else SA_LAUNCH(16);
+#undef SA_LAUNCH
+    int code = msgl_check_launch();
+    if (code != MSGL_OK || splits <= 1) return code;
+    const int N = n_q * dv;
+    const dim3 g2(T_, max(1, min((N + 255) / 256, 16)));
+    if (dtype == MSGL_F32) sum_pieces_kernel<float><<<g2, 256, 0, stream>>>(part, kv_len, nullptr, (float*)out, out_stride, T_, N, splits, split_keys);
+    else sum_pieces_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>(part, kv_len, nullptr, (__nv_bfloat16*)out, out_stride, T_, N, splits, split_keys);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// minGRU: a gated recurrence per channel whose gates read the current token only
+//
+//   z = sigmoid(pz + bz), a = px + bx, c = a + 1/2 (a >= 0) or sigmoid(a) (a < 0)
+//   S_t = (1 - z_t) S_(t-1) + z_t c_t;   out_t = S_t * silu(pg_t) * c_out
+//   pz, px, pg: columns of one packed projection; state [slot][W] float32
+// One thread per (request, channel) walks the request's tokens of the step in order.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void mingru_kernel(const void* proj_, long long stride, int z_off, int x_off, int g_off, int W,
+                              const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
+                              const int* __restrict__ q_start, const int* __restrict__ slots, void* out_, long long out_stride,
+                              float c_out) {
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    if (n <= 0) return;
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    T* out = reinterpret_cast<T*>(out_);
+    float* Sp = state + (size_t)slots[r] * W + c;
+    float S = *Sp;
+    const float b_z = bz[c], b_x = bx[c];
+    const T* row = proj + (size_t)t0 * stride;
+    float pz = to_f32<T>(row[z_off + c]), px = to_f32<T>(row[x_off + c]), pg = to_f32<T>(row[g_off + c]);
+    for (int tt = 0; tt < n; ++tt) {
+        float nz = 0.f, nx = 0.f, ng = 0.f;
+        if (tt + 1 < n) {                              // the next token's numbers are on their way while this one is computed
+            const T* nrow = proj + (size_t)(t0 + tt + 1) * stride;
+            nz = to_f32<T>(nrow[z_off + c]); nx = to_f32<T>(nrow[x_off + c]); ng = to_f32<T>(nrow[g_off + c]);
+        }
+        const float z = sigmoidf_(pz + b_z), a = px + b_x;
+        const float cand = a >= 0.f ? a + 0.5f : sigmoidf_(a);
+        S = (1.f - z) * S + z * cand;
+        out[(size_t)(t0 + tt) * out_stride + c] = from_f32<T>(S * siluf_(pg) * c_out);
+        pz = nz; px = nx; pg = ng;
+    }
+    *Sp = S;
+}
+
+MSGL_API int msgl_mingru(const void* proj, long long stride, int z_off, int x_off, int g_off, int W, const float* bz, const float* bx,
+                         float* state, const int* q_start, const int* slots, void* out, long long out_stride, float c_out, int B,
+                         int dtype, cudaStream_t stream) {
+    if (B <= 0) return MSGL_OK;
+    if (W <= 0) return MSGL_ERR_SIZE;
+    const int threads = 64;
+    const dim3 grid((W + threads - 1) / threads, B);
+    if (dtype == MSGL_F32) mingru_kernel<float><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, out, out_stride, c_out);
+    else if (dtype == MSGL_BF16) mingru_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, out, out_stride, c_out);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out = c * (a / rms(a) * wa + b / rms(b) * wb) in float32: the outputs of two mixers joined, each normed over the row
+// One block per token.
+// ---------------------------------------------------------------------------------------
+template <typename A>
+__global__ void __launch_bounds__(256) pair_norm_kernel(const A* __restrict__ a, const A* __restrict__ b, const float* __restrict__ wa,
+                                                        const float* __restrict__ wb, float eps, float c, float* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    const size_t t = blockIdx.x;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = to_f32<A>(a[t * H + i]), y = to_f32<A>(b[t * H + i]);
+        sa = fmaf(x, x, sa); sb = fmaf(y, y, sb);
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float fa = rsqrtf(sa / (float)H + eps) * c, fb = rsqrtf(sb / (float)H + eps) * c;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[t * H + i] = to_f32<A>(a[t * H + i]) * fa * wa[i] + to_f32<A>(b[t * H + i]) * fb * wb[i];
+}
+
+MSGL_API int msgl_pair_norm(const void* a, const void* b, int in_is_f32, const float* wa, const float* wb, float eps, float c, float* out,
+                            int T_, int H, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (H <= 0) return MSGL_ERR_SIZE;
+    if (in_is_f32) pair_norm_kernel<float><<<T_, 256, 0, stream>>>((const float*)a, (const float*)b, wa, wb, eps, c, out, H);
+    else pair_norm_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, eps, c, out, H);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Short causal convolution per channel with bias and an activation, continued from the request's last inputs
+//
+//   y[t, c] = act(bias[c] + sum_j w[j][c] * u[t - (K - 1) + j, c]);  w comes transposed, [K][C], the oldest input's tap first;
+//   inputs before the step's first token come from state [slot][K - 1][C] (oldest first; zero when the request was opened)
+// One thread per (token, channel).  conv_state_shift_kernel then moves the request's last K - 1 inputs into the state.
+// ---------------------------------------------------------------------------------------
+#define CV_MAX_TAPS 16
+template <typename T>
+__global__ void causal_conv_act_kernel(const void* in_, long long stride, int off, int C, int K, const float* __restrict__ w,
+                                       const float* __restrict__ bias, const void* state_, const int* __restrict__ token_req,
+                                       const int* __restrict__ q_start, const int* __restrict__ slots, void* out_, int act) {
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const T* in = reinterpret_cast<const T*>(in_);
+    const T* state = reinterpret_cast<const T*>(state_);
+    const int r = token_req[t];
+    const int local = t - q_start[r];
+    const int slot = slots[r];
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int li = local - (K - 1) + j;              // place of the input among the step's tokens of the request
+        float u;
+        if (li >= 0) u = to_f32<T>(in[(size_t)(t - (K - 1) + j) * stride + off + c]);
+        else u = to_f32<T>(state[((size_t)slot * (K - 1) + (K - 1 + li)) * C + c]);
+        acc = fmaf(w[(size_t)j * C + c], u, acc);
+    }
+    if (act == 0) acc = siluf_(acc);
+    reinterpret_cast<T*>(out_)[(size_t)t * C + c] = from_f32<T>(acc);
+}
+
+template <typename T>
+__global__ void conv_state_shift_kernel(const void* in_, long long stride, int off, int C, int K, void* state_,
+                                        const int* __restrict__ q_start, const int* __restrict__ slots) {
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const T* in = reinterpret_cast<const T*>(in_);
+    T* state = reinterpret_cast<T*>(state_) + (size_t)slots[r] * (K - 1) * C;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    if (n <= 0) return;
+    for (int i = 0; i < K - 1; ++i) {                    // row i of the new state is row i + n of [old state; the step's inputs]
+        const int s = i + n;
+        state[(size_t)i * C + c] = s < K - 1 ? state[(size_t)s * C + c] : in[(size_t)(t0 + s - (K - 1)) * stride + off + c];
+    }
+}
+
+MSGL_API int msgl_causal_conv_act(const void* in, long long stride, int off, int C, int K, const float* w, const float* bias, void* state,
+                                  const int* token_req, const int* q_start, const int* slots, void* out, int act, int T_, int B,
+                                  int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (C <= 0 || K < 1 || K > CV_MAX_TAPS || (K > 1 && state == nullptr)) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int threads = 128;
+    const dim3 grid((C + threads - 1) / threads, T_);
+    if (dtype == MSGL_F32) causal_conv_act_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
+    else causal_conv_act_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
+    int code = msgl_check_launch();
+    if (code != MSGL_OK || K == 1) return code;
+    const dim3 g2((C + threads - 1) / threads, B);
+    if (dtype == MSGL_F32) conv_state_shift_kernel<float><<<g2, threads, 0, stream>>>(in, stride, off, C, K, state, q_start, slots);
+    else conv_state_shift_kernel<__nv_bfloat16><<<g2, threads, 0, stream>>>(in, stride, off, C, K, state, q_start, slots);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// State-space scan, token by token
+//
+//   per head h (group g = h / (heads / groups)), state S [N][P] float32 per request:
+//     dt = softplus(pdt[t, h] + dt_bias[h]);  S <- exp(-exp(A_log[h]) * dt) * S + dt * B[t, g, :] x[t, h, :]^T
+//     y[t, h, :] = S^T C[t, g, :] + D[h] * x[t, h, :]
+//   xbc row [T][heads * P | groups * N | groups * N] (what the convolution left); pdt a column range of the packed projection
+// A block owns SS_COLS columns of one (request, head) state and walks the request's tokens in order; SS_PARTS threads share
+// a column's rows.
+// ---------------------------------------------------------------------------------------
+#define SS_COLS 32
+#define SS_PARTS 8
+#define SS_MAX_ROWS 64      // state sizes up to SS_PARTS * SS_MAX_ROWS
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(SS_COLS * SS_PARTS)
+ssm_scan_kernel(const void* xbc_, int heads, int groups, int N, int P, const void* proj_, long long stride, int dt_off,
+                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y) {
+    extern __shared__ float bc[];                    // [2][2][N]: double-buffered B and C of the current token
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SS_COLS;
+    const int tid = threadIdx.x;
+    const int part = tid & (SS_PARTS - 1), col = col0 + (tid >> 3);
+    const bool col_ok = col < P;
+    const int t0 = q_start[r], n = q_start[r + 1] - t0;
+    if (n <= 0) return;
+    const int g = h / (heads / groups);
+    const int inner = heads * P, C_ = inner + 2 * groups * N;
+    const T* xbc = reinterpret_cast<const T*>(xbc_);
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    float* S = state + (((size_t)slots[r] * heads + h) * N) * P;
+    const int rows = (N + SS_PARTS - 1) / SS_PARTS;
+    float s[NR];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + SS_PARTS * j;
+        s[j] = (j < rows && i < N && col_ok) ? S[(size_t)i * P + col] : 0.f;
+    }
+    const float a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
+    for (int tt = 0; tt < n; ++tt) {
+        const size_t row = (size_t)(t0 + tt) * C_;
+        float* Bb = bc + (tt & 1) * 2 * N;
+        float* Cb = Bb + N;
+        for (int i = tid; i < N; i += SS_COLS * SS_PARTS) {
+            Bb[i] = to_f32<T>(xbc[row + inner + g * N + i]);
+            Cb[i] = to_f32<T>(xbc[row + inner + groups * N + g * N + i]);
+        }
+        const float x = col_ok ? to_f32<T>(xbc[row + h * P + col]) : 0.f;
+        const float dt = softplusf_(to_f32<T>(proj[(size_t)(t0 + tt) * stride + dt_off + h]) + bias);
+        const float decay = expf(a * dt), dx = dt * x;
+        __syncthreads();
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            if (j < rows) {
+                const int i = part + SS_PARTS * j;
+                if (i < N) {
+                    s[j] = fmaf(decay, s[j], Bb[i] * dx);
+                    acc = fmaf(s[j], Cb[i], acc);
+                }
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        if (part == 0 && col_ok) y[(size_t)(t0 + tt) * inner + h * P + col] = acc + dskip * x;
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int i = part + SS_PARTS * j;
+        if (j < rows && i < N && col_ok) S[(size_t)i * P + col] = s[j];
+    }
+}
+
+MSGL_API int msgl_ssm_scan(const void* xbc, int heads, int groups, int N, int P, const void* proj, long long stride, int dt_off,
+                           const float* dt_bias, const float* A_log, const float* Dskip, float* state, const int* q_start,
+                           const int* slots, float* y, int B, int dtype, cudaStream_t stream) {
+    if (B <= 0) return MSGL_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || N > SS_PARTS * SS_MAX_ROWS) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const dim3 grid(B, heads, (P + SS_COLS - 1) / SS_COLS);
+    const size_t smem = (size_t)4 * N * sizeof(float);
+    const int nr = (N + SS_PARTS - 1) / SS_PARTS;
+#define SS_LAUNCH(NRR)                                                                                                          \
+    do {                                                                                                                        \
+        if (dtype == MSGL_F32)                                                                                                  \
+            ssm_scan_kernel<float, NRR><<<grid, SS_COLS * SS_PARTS, smem, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias, \
+                                                                                  A_log, Dskip, state, q_start, slots, y);      \
+        else                                                                                                                    \
+            ssm_scan_kernel<__nv_bfloat16, NRR><<<grid, SS_COLS * SS_PARTS, smem, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off,  \
+                                                                                          dt_bias, A_log, Dskip, state, q_start, slots, y); \
+    } while (0)
+    if (nr <= 4) SS_LAUNCH(4);
+    else if (nr <= 8) SS_LAUNCH(8);
+    else if (nr <= 16) SS_LAUNCH(16);
+    else if (nr <= 32) SS_LAUNCH(32);
+    else SS_LAUNCH(64);
+#undef SS_LAUNCH
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out = (y * silu(z)) / rms over each of `parts` equal parts of the row * w * c:  the gate comes BEFORE the norm
+//   y float32 [T, N] contiguous; z and out [T, N] views into packed rows of the activation type; w float32 [N]
+// One warp per (token, part).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_group_norm_kernel(const float* __restrict__ y, int N, int parts, const float* __restrict__ w, float eps,
+                                       const void* z_, long long z_stride, void* out_, long long out_stride, float c, int T_) {
+    const long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wi >= (long long)T_ * parts) return;
+    const int t = (int)(wi / parts), g = (int)(wi - (long long)t * parts);
+    const int n = N / parts;
+    const float* yr = y + (size_t)t * N + (size_t)g * n;
+    const T* zr = reinterpret_cast<const T*>(z_) + (size_t)t * z_stride + (size_t)g * n;
+    T* orow = reinterpret_cast<T*>(out_) + (size_t)t * out_stride + (size_t)g * n;
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) { const float v = yr[i] * siluf_(to_f32<T>(zr[i])); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss / (float)n + eps) * c;
+    for (int i = lane; i < n; i += 32)
+        orow[i] = from_f32<T>(yr[i] * siluf_(to_f32<T>(zr[i])) * f * w[(size_t)g * n + i]);
+}
+
+MSGL_API int msgl_gate_group_norm(const float* y, int N, int parts, const float* w, float eps, const void* z, long long z_stride,
+                                  void* out, long long out_stride, float c, int T_, int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (N <= 0 || parts <= 0 || N % parts) return MSGL_ERR_SIZE;
+    const long long warps = (long long)T_ * parts;
+    const unsigned grid = (unsigned)((warps + 7) / 8);
+    if (dtype == MSGL_F32) gate_group_norm_kernel<float><<<grid, 256, 0, stream>>>(y, N, parts, w, eps, z, z_stride, out, out_stride, c, T_);
+    else if (dtype == MSGL_BF16) gate_group_norm_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(y, N, parts, w, eps, z, z_stride, out, out_stride, c, T_);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// out = act(x) * c, act: 0 silu, 1 gelu_tanh, 2 sigmoid, 3 relu(x)^2, 4 relu; [T, N] views with row strides of their own
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, long long x_stride, T* __restrict__ out, long long out_stride, int N, int act, float c) {
+    const size_t t = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x) {
+        const float v = to_f32<T>(x[t * x_stride + i]);
+        float a;
+        switch (act) {
+            case 0: a = siluf_(v); break;
+            case 1: a = gelu_tanhf_(v); break;
+            case 2: a = sigmoidf_(v); break;
+            case 3: a = v > 0.f ? v * v : 0.f; break;
+            default: a = fmaxf(v, 0.f); break;
+        }
+        out[t * out_stride + i] = from_f32<T>(a * c);
+    }
+}
+
+MSGL_API int msgl_unary_act(const void* x, long long x_stride, void* out, long long out_stride, int N, int act, float c, int T_, int dtype,
+                            cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (N <= 0 || act < 0 || act > 4) return MSGL_ERR_SIZE;
+    const dim3 grid(max(1, min((N + 255) / 256, 64)), T_);
+    if (dtype == MSGL_F32) unary_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, x_stride, (float*)out, out_stride, N, act, c);
+    else if (dtype == MSGL_BF16) unary_act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, N, act, c);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Router of a mixture of experts: one block per token
+//
+//   z = W h (float32 sums), s = sigmoid(z), choice = s + correction
+//   the experts form `n_groups` equal groups of neighbours; a group's score is the sum of its two largest choice scores; only
+//   experts of the `keep` best groups can be chosen; the `top` largest choice scores among them are chosen (the lower index
+//   wins a tie); weights = the chosen experts' s over their sum (+ 1e-20)
+//   -> idx int32 [T, top], wts float32 [T, top]
+// ---------------------------------------------------------------------------------------
+#define RT_MAX_EXPERTS 1024
+#define RT_MAX_GROUPS 64
+template <typename T>
+__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ W,
+                                                    const float* __restrict__ correction, int H, int E, int n_groups, int keep,
+                                                    int top, int* __restrict__ idx, float* __restrict__ wts) {
+    __shared__ float s_sh[RT_MAX_EXPERTS], c_sh[RT_MAX_EXPERTS], g_sh[RT_MAX_GROUPS];
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const T* hr = h + (size_t)t * h_stride;
+    for (int e = warp; e < E; e += nw) {
+        const T* wr = W + (size_t)e * H;
+        float acc = 0.f;
+        for (int i = lane; i < H; i += 32) acc = fmaf(to_f32<T>(wr[i]), to_f32<T>(hr[i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float s = sigmoidf_(acc);
+            s_sh[e] = s;
+            c_sh[e] = s + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    const int per = E / n_groups;
+    if (keep < n_groups) {
+        for (int g = tid; g < n_groups; g += blockDim.x) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+            for (int i = 0; i < per; ++i) {
+                const float v = c_sh[g * per + i];
+                if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v;
+            }
+            g_sh[g] = per >= 2 ? m1 + m2 : m1;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            // the groups that are not among the `keep` best lose their experts
+            for (int k = 0; k < keep; ++k) {
+                int best = -1; float bv = -INFINITY;
+                for (int g = 0; g < n_groups; ++g)
+                    if (!isnan(g_sh[g]) && (best < 0 || g_sh[g] > bv)) { best = g; bv = g_sh[g]; }
+                if (best >= 0) g_sh[best] = NAN;          // taken
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < E; e += blockDim.x)
+            if (!isnan(g_sh[e / per])) c_sh[e] = -INFINITY;
+        __syncthreads();
+    }
+    if (warp == 0) {
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float bv = -INFINITY; int be = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = c_sh[e];
+                if (!isnan(v) && (v > bv || (v == bv && e < be))) { bv = v; be = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            if (be >= E) be = 0;                          // nothing left to choose from (top > experts allowed): refused on the host
+            if (lane == 0) { idx[(size_t)t * top + k] = be; c_sh[be] = NAN; }
+            total += s_sh[be];
+            __syncwarp();
+        }
+        const float inv = 1.f / (total + 1e-20f);
+        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = s_sh[idx[(size_t)t * top + k]] * inv;
+    }
+}
+
+MSGL_API int msgl_route(const void* h, long long h_stride, const void* W, const float* correction, int H, int E, int n_groups, int keep,
+                        int top, int* idx, float* wts, int T_, int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (H <= 0 || E <= 0 || E > RT_MAX_EXPERTS || n_groups < 1 || n_groups > RT_MAX_GROUPS || E % n_groups || keep < 1 || keep > n_groups ||
+        top < 1 || top > keep * (E / n_groups))
+        return MSGL_ERR_SIZE;
+    if (dtype == MSGL_F32) route_kernel<float><<<T_, 128, 0, stream>>>((const float*)h, h_stride, (const float*)W, correction, H, E, n_groups, keep, top, idx, wts);
+    else if (dtype == MSGL_BF16) route_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)W, correction, H, E, n_groups, keep, top, idx, wts);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// The chosen experts' products for a few tokens, straight from the stacked weights
+//
+//   act[t * top + k, r] = silu(Wg[e][r] . h_t) * (Wu[e][r] . h_t),  e = idx[t, k];   Wgu [E][2][F][H] = an expert's gate, then its up
+//   out[t, c] = c_out * sum_k wts[t, k] * (Wd[e_k][c] . act[t * top + k, :]) in float32;   Wd [E][H][F]
+// One warp per output row of a (token, choice) pair, resp. per output column of a token.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) expert_gate_up_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ Wgu,
+                                                             const int* __restrict__ idx, int top, int H, int F, T* __restrict__ act) {
+    const int pair = blockIdx.y, t = pair / top;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= F) return;
+    const int e = idx[pair];
+    const T* hr = h + (size_t)t * h_stride;
+    const T* g = Wgu + ((size_t)e * 2 * F + r) * H;
+    const T* u = g + (size_t)F * H;
+    float ag = 0.f, au = 0.f;
+    for (int i = lane; i < H; i += 32) {
+        const float x = to_f32<T>(hr[i]);
+        ag = fmaf(to_f32<T>(g[i]), x, ag);
+        au = fmaf(to_f32<T>(u[i]), x, au);
+    }
+    ag = warp_sum(ag); au = warp_sum(au);
+    if (lane == 0) act[(size_t)pair * F + r] = from_f32<T>(siluf_(ag) * au);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) expert_down_kernel(const T* __restrict__ act, const T* __restrict__ Wd, const int* __restrict__ idx,
+                                                          const float* __restrict__ wts, int top, int H, int F, float c_out,
+                                                          float* __restrict__ out) {
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (c >= H) return;
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = idx[(size_t)t * top + k];
+        const T* w = Wd + ((size_t)e * H + c) * F;
+        const T* a = act + ((size_t)t * top + k) * F;
+        float acc = 0.f;
+        for (int i = lane; i < F; i += 32) acc = fmaf(to_f32<T>(w[i]), to_f32<T>(a[i]), acc);
+        acc = warp_sum(acc);
+        total = fmaf(wts[(size_t)t * top + k], acc, total);
+    }
+    if (lane == 0) out[(size_t)t * H + c] = total * c_out;
+}
+
+MSGL_API int msgl_experts_few(const void* h, long long h_stride, const void* Wgu, const void* Wd, const int* idx,
+                              const float* wts, int top, int H, int F, void* act, float c_out, float* out, int T_, int dtype,
+                              cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (top < 1 || H <= 0 || F <= 0) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const dim3 g1((F + 7) / 8, T_ * top), g2((H + 7) / 8, T_);
+    if (dtype == MSGL_F32) {
+        expert_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, h_stride, (const float*)Wgu, idx, top, H, F, (float*)act);
+        expert_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)act, (const float*)Wd, idx, wts, top, H, F, c_out, out);
+    } else {
+        expert_gate_up_kernel<__nv_bfloat16><<<g1, 256, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)Wgu, idx, top, H, F,
+                                                                      (__nv_bfloat16*)act);
+        expert_down_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)Wd, idx, wts, top, H, F, c_out, out);
+    }
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Many tokens: the (token, choice) pairs in the order of their experts
+//
+//   expert_count_kernel   counts[e] = pairs whose expert is e                                   (one block per expert)
+//   expert_place_kernel   place[pair] = row of the pair in expert order, stable within an expert  (one block per expert)
+//   expert_gather_kernel  rows[place[pair]] = h[token of the pair]
+//   expert_combine_kernel out[t] = c * sum_k wts[t, k] * y[place[t * top + k]] in float32
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) expert_count_kernel(const int* __restrict__ idx, int n_pairs, int* __restrict__ counts) {
+    __shared__ float scratch[32];
+    const int e = blockIdx.x;
+    int n = 0;
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) n += idx[i] == e;
+    const float total = block_sum((float)n, scratch);          // exact below 2^24 pairs
+    if (threadIdx.x == 0) counts[e] = (int)(total + 0.5f);
+}
+
+__global__ void __launch_bounds__(256) expert_place_kernel(const int* __restrict__ idx, int n_pairs, const int* __restrict__ counts,
+                                                           int* __restrict__ place) {
+    __shared__ int warp_tot[8];
+    __shared__ int base_sh;
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        int b = 0;
+        for (int i = 0; i < e; ++i) b += counts[i];
+        base_sh = b;
+    }
+    __syncthreads();
+    int base = base_sh;
+    for (int i0 = 0; i0 < n_pairs; i0 += 256) {
+        const int i = i0 + tid;
+        const bool mine = i < n_pairs && idx[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_tot[warp] = __popc(m);
+        __syncthreads();
+        int before = 0, all = 0;
+        for (int w = 0; w < 8; ++w) { if (w < warp) before += warp_tot[w]; all += warp_tot[w]; }
+        if (mine) place[i] = base + before + __popc(m & ((1u << lane) - 1u));
+        base += all;
+        __syncthreads();
+    }
+}
+
+template <typename T>
+__global__ void expert_gather_kernel(const T* __restrict__ h, long long h_stride, const int* __restrict__ place, int top, int H,
+                                     T* __restrict__ rows) {
+    const int pair = blockIdx.x, t = pair / top;
+    const T* src = h + (size_t)t * h_stride;
+    T* dst = rows + (size_t)place[pair] * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+template <typename Y>
+__global__ void expert_combine_kernel(const Y* __restrict__ y, const int* __restrict__ place, const float* __restrict__ wts, int top, int H,
+                                      float c, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wts[(size_t)t * top + k], to_f32<Y>(y[(size_t)place[(size_t)t * top + k] * H + i]), acc);
+        out[(size_t)t * H + i] = acc * c;
+    }
+}
+
+MSGL_API int msgl_expert_order(const int* idx, int n_pairs, int E, int* counts, int* place, cudaStream_t stream) {
+    if (n_pairs <= 0) return MSGL_OK;
+    if (E <= 0 || n_pairs >= (1 << 24)) return MSGL_ERR_SIZE;
+    expert_count_kernel<<<E, 256, 0, stream>>>(idx, n_pairs, counts);
+    expert_place_kernel<<<E, 256, 0, stream>>>(idx, n_pairs, counts, place);
+    return msgl_check_launch();
+}
+
+MSGL_API int msgl_expert_gather(const void* h, long long h_stride, const int* place, int top, int H, void* rows, int n_pairs, int dtype,
+                                cudaStream_t stream) {
+    if (n_pairs <= 0) return MSGL_OK;
+    if (dtype == MSGL_F32) expert_gather_kernel<float><<<n_pairs, 128, 0, stream>>>((const float*)h, h_stride, place, top, H, (float*)rows);
+    else if (dtype == MSGL_BF16) expert_gather_kernel<__nv_bfloat16><<<n_pairs, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, place, top, H, (__nv_bfloat16*)rows);
+    else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+MSGL_API int msgl_expert_combine(const void* y, int y_is_f32, const int* place, const float* wts, int top, int H, float c, float* out,
+                                 int T_, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (y_is_f32) expert_combine_kernel<float><<<T_, 256, 0, stream>>>((const float*)y, place, wts, top, H, c, out);
+    else expert_combine_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)y, place, wts, top, H, c, out);
+    return msgl_check_launch();
+}

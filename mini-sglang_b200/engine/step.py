@@ -95,7 +95,8 @@ class CacheStorage:
                 g = mgr.groups[mgr.group_of_cache[cid]]
                 shape = (g.pool.num_pages + 1, need.n_kv_heads, mgr.page_size, need.head_dim)
                 k = torch.zeros(shape, dtype=dtype, device=device)
-                self.kv[cid] = (k, k if need.shared_kv else torch.zeros(shape, dtype=dtype, device=device))
+                v_shape = shape[:3] + (need.v_head_dim or need.head_dim,)
+                self.kv[cid] = (k, k if need.shared_kv else torch.zeros(v_shape, dtype=dtype, device=device))
             elif isinstance(need, StateNeed):
                 dt = {"float32": torch.float32, "compute": dtype, "int32": torch.int32}[need.dtype]
                 self.state[cid] = torch.zeros((mgr.max_reqs + 1, *need.shape), dtype=dt, device=device)
@@ -109,14 +110,14 @@ class CacheStorage:
             t[slot].zero_()
 
     def bytes(self) -> int:
-        n = sum(k.numel() * k.element_size() * (1 if v is k else 2) for k, v in self.kv.values())
+        n = sum(k.numel() * k.element_size() + (0 if v is k else v.numel() * v.element_size()) for k, v in self.kv.values())
         return n + sum(t.numel() * t.element_size() for t in self.state.values())
 
 
 def kv_bytes_per_page(needs: Dict[int, object], page_size: int, dtype: torch.dtype) -> int:
     item = torch.empty((), dtype=dtype).element_size()
-    return sum((1 if n.shared_kv else 2) * page_size * n.n_kv_heads * n.head_dim * item for n in needs.values()
-               if isinstance(n, PagedKVNeed))
+    return sum(page_size * n.n_kv_heads * (n.head_dim + (0 if n.shared_kv else (n.v_head_dim or n.head_dim))) * item
+               for n in needs.values() if isinstance(n, PagedKVNeed))
 
 
 class _Graph:

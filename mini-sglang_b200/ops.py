@@ -1037,6 +1037,316 @@ def group_rms_gate(x: torch.Tensor, heads: int, weight: torch.Tensor, eps: float
 
 
 # ---------------------------------------------------------------------------------------
+# sigmoid attention, gated recurrences, state-space scan, routed experts (csrc/mixers_gated.cu)
+# ---------------------------------------------------------------------------------------
+_gated = None
+ACT_RELU2, ACT_RELU = 3, 4
+SIGMOID_ATTENTION_ROWS = 8          # (token, head) rows of a block of the sigmoid attention kernel
+SIGMOID_ATTENTION_MAX_HEAD_DIM = 512
+SIGMOID_ATTENTION_SPLIT_KEYS = 256  # keys of a piece when a one-token step cuts a request's keys over several blocks
+SSM_MAX_STATE = 512
+ROUTE_MAX_EXPERTS, ROUTE_MAX_GROUPS = 1024, 64
+EXPERTS_FEW_PAIRS = 64              # up to this many (token, choice) pairs the experts' products stream the weights
+
+
+def _gated_lib():
+    global _gated
+    if _gated is None:
+        lib = _build.gated_mixers_library()
+        lib.msgl_embed_positions.argtypes = [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        lib.msgl_headnorm_kvwrite.argtypes = [c_void_p, c_ll] + [c_int] * 7 + [c_void_p, c_void_p, c_float, c_float, c_int] + \
+            [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]
+        lib.msgl_sigmoid_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p] + \
+            [c_int] * 11 + [c_float, c_int, c_void_p]
+        lib.msgl_mingru.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int] + [c_void_p] * 6 + [c_ll, c_float, c_int, c_int, c_void_p]
+        lib.msgl_pair_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_causal_conv_act.argtypes = [c_void_p, c_ll, c_int, c_int, c_int] + [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p]
+        lib.msgl_ssm_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int] + [c_void_p] * 7 + [c_int, c_int, c_void_p]
+        lib.msgl_gate_group_norm.argtypes = [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_float, c_int,
+                                             c_int, c_void_p]
+        lib.msgl_unary_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p]
+        lib.msgl_route.argtypes = [c_void_p, c_ll, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_experts_few.argtypes = [c_void_p, c_ll] + [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
+                                                                            c_void_p]
+        lib.msgl_expert_order.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        lib.msgl_expert_gather.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_expert_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p]
+        _gated = lib
+    return _gated
+
+
+def _col_off(view: torch.Tensor, base: torch.Tensor) -> int:
+    """Column at which `view` starts inside the packed rows that `base` starts."""
+    return (view.data_ptr() - base.data_ptr()) // base.element_size()
+
+
+def embed_positions(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, places: torch.Tensor, scale: float) -> torch.Tensor:
+    """ids, positions int32 [T]; table [V, H], places [P, H] -> float32 [T, H] = float(table[ids]) * scale + float(places[positions])."""
+    _need_cuda(ids, positions, table, places)
+    T, (V, H) = ids.numel(), table.shape
+    assert ids.dtype == torch.int32 and positions.dtype == torch.int32 and table.is_contiguous() and places.is_contiguous()
+    assert places.shape[1] == H and places.dtype == table.dtype
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(_gated_lib().msgl_embed_positions(_ptr(ids), _ptr(positions), _ptr(table), _ptr(places), _ptr(out), T, H, V, places.shape[0],
+                                             float(scale), _dt(table), _stream()), "embed_positions")
+    return out
+
+
+def headnorm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, *, n_q: int, n_kv: int, q_weight: torch.Tensor,
+                     k_weight: torch.Tensor, eps: float, temp_coef: float, temp_every: int, positions: torch.Tensor,
+                     out_loc: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                     page_size: int) -> torch.Tensor:
+    """q_in [T, n_q * d], k_in [T, n_kv * d], v_in [T, n_kv * dv]: views into one packed projection.  Every head of q and of k is
+    RMS-normed by itself with one weight [d] for all heads (float32); q is then multiplied by 1 + temp_coef * ln(floor((position +
+    1) / temp_every) + 1) (temp_coef 0: not).  The normed k goes to `k_cache` [pages, n_kv, page, d], v as it is to `v_cache`
+    [pages, n_kv, page, dv] at token slots `out_loc`; the q rows come back as [T, n_q, d]."""
+    _need_cuda(q_in, k_in, v_in, q_weight, k_weight, positions, out_loc, k_cache, v_cache)
+    T = q_in.shape[0]
+    d, dv = q_in.shape[1] // n_q, v_in.shape[1] // n_kv
+    stride = _rows_view(q_in, n_q * d, "q")
+    assert _rows_view(k_in, n_kv * d, "k") == stride and _rows_view(v_in, n_kv * dv, "v") == stride and q_in.dtype == k_in.dtype == v_in.dtype
+    assert q_weight.dtype == torch.float32 and k_weight.dtype == torch.float32 and q_weight.numel() == d and k_weight.numel() == d
+    assert positions.dtype == torch.int32 and positions.numel() >= T
+    if k_cache is not None:
+        assert k_cache.dtype == q_in.dtype and v_cache.dtype == q_in.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (n_kv, page_size, d) and tuple(v_cache.shape[1:]) == (n_kv, page_size, dv)
+        assert out_loc is not None and out_loc.dtype == torch.int32 and out_loc.numel() >= T
+    else:
+        out_loc = None
+    q_out = torch.empty((T, n_q, d), dtype=q_in.dtype, device=q_in.device)
+    code = _gated_lib().msgl_headnorm_kvwrite(_ptr(q_in), stride, 0, _col_off(k_in, q_in), _col_off(v_in, q_in), n_q, n_kv, d, dv,
+                                              _ptr(q_weight), _ptr(k_weight), float(eps), float(temp_coef), int(temp_every),
+                                              _ptr(positions), _ptr(out_loc), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, T,
+                                              _dt(q_in), _stream())
+    _check(code, "headnorm_kvwrite")
+    return q_out
+
+
+def sigmoid_attention_geometry(n_q: int, n_kv: int) -> Tuple[int, int]:
+    """(tokens per query tile, query heads of one kv head per block) of the sigmoid attention kernel."""
+    G = n_q // n_kv
+    gh = min(G, SIGMOID_ATTENTION_ROWS)
+    return SIGMOID_ATTENTION_ROWS // gh, gh
+
+
+def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, q_start: torch.Tensor,
+                      kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int, scale: float, bias: torch.Tensor,
+                      q_lens: Optional[Sequence[int]], workspace=None) -> None:
+    """Causal attention over the paged cache whose weight of key j for the query at position i is sigmoid(q . k * scale +
+    bias[head][min(i - j, L - 1)]), each key by itself (nothing is normed over the keys).  q [T, heads, d]; K cache [pages, n_kv,
+    page, d], V cache [pages, n_kv, page, dv]; bias float32 [heads, L]; out [T, heads * dv] (may be a view into packed rows).
+    q_lens: the requests' numbers of tokens as the host knows them (they size the launch), or None when every request brings one
+    token: the keys are then cut into pieces of SIGMOID_ATTENTION_SPLIT_KEYS for as many blocks as the block table's width asks
+    for, whose sums are added in order (workspace: a parts.Workspace for the pieces)."""
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, bias)
+    T, n_q, d = q.shape
+    dv = v_cache.shape[3]
+    assert q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
+    out_stride = _rows_view(out, n_q * dv, "out")
+    B = kv_len.numel()
+    QT, GH = sigmoid_attention_geometry(n_q, n_kv)
+    assert bias.dtype == torch.float32 and bias.dim() == 2 and bias.shape[0] == n_q and bias.is_contiguous()
+    uniform = q_lens is None
+    n_tiles = B if uniform else sum(-(-n // QT) for n in q_lens)
+    splits, part = 1, None
+    if uniform:
+        splits = max(1, -(-(block_table.shape[1] * page_size) // SIGMOID_ATTENTION_SPLIT_KEYS))
+        if splits > 1:
+            numel = splits * T * n_q * dv
+            part = workspace.get("sigmoid_attention_pieces", numel, torch.float32) if workspace is not None else \
+                torch.empty(numel, dtype=torch.float32, device=q.device)
+    code = _gated_lib().msgl_sigmoid_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+        n_tiles, _ptr(bias), bias.shape[1], _ptr(out), out_stride, _ptr(part), splits, SIGMOID_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv,
+        d, dv, page_size, QT, GH, float(scale), _dt(q), _stream())
+    _check(code, f"sigmoid_attention (head sizes {d}, {dv})")
+    if splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1
+
+
+def mingru(z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, z_bias: torch.Tensor, x_bias: torch.Tensor, *, state: torch.Tensor,
+           q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """A gated recurrence per channel over the step's tokens, continued from and written back to `state` [slots, W] float32:
+    zz = sigmoid(z + z_bias), a = x + x_bias, c = a + 1/2 where a >= 0 and sigmoid(a) below, S <- (1 - zz) S + zz c;
+    out = S * silu(g) * scale.  z, x, g [T, W]: views into one packed projection; out [T, W] (may be a view)."""
+    _need_cuda(z, x, g, z_bias, x_bias, state, q_start, slots, out)
+    T, W = z.shape
+    stride = _rows_view(z, W, "z")
+    assert _rows_view(x, W, "x") == stride and _rows_view(g, W, "g") == stride and z.dtype == x.dtype == g.dtype == out.dtype
+    assert z_bias.dtype == torch.float32 and x_bias.dtype == torch.float32 and z_bias.numel() == W and x_bias.numel() == W
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (W,)
+    B = q_start.numel() - 1
+    code = _gated_lib().msgl_mingru(_ptr(z), stride, 0, _col_off(x, z), _col_off(g, z), W, _ptr(z_bias), _ptr(x_bias), _ptr(state),
+                                    _ptr(q_start), _ptr(slots), _ptr(out), _rows_view(out, W, "out"), float(scale), B, _dt(z), _stream())
+    _check(code, "mingru")
+
+
+def pair_norm(a: torch.Tensor, b: torch.Tensor, a_weight: torch.Tensor, b_weight: torch.Tensor, eps: float, scale: float) -> torch.Tensor:
+    """-> float32 [T, H] = scale * (a / rms(a) * a_weight + b / rms(b) * b_weight), each row normed by itself; a, b [T, H] float32 or
+    bfloat16 (both alike), weights float32 [H]."""
+    _need_cuda(a, b, a_weight, b_weight)
+    T, H = a.shape
+    assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype
+    assert a_weight.dtype == torch.float32 and b_weight.dtype == torch.float32 and a_weight.numel() == H and b_weight.numel() == H
+    _dt(a)
+    out = torch.empty((T, H), dtype=torch.float32, device=a.device)
+    _check(_gated_lib().msgl_pair_norm(_ptr(a), _ptr(b), int(a.dtype == torch.float32), _ptr(a_weight), _ptr(b_weight), float(eps),
+                                       float(scale), _ptr(out), T, H, _stream()), "pair_norm")
+    return out
+
+
+def causal_conv_act(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], *, state: Optional[torch.Tensor],
+                    token_req: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, act: int = ACT_SILU) -> torch.Tensor:
+    """Short causal convolution over time on every channel of x [T, C] (a view into packed rows) with taps [K, C] (float32, the
+    oldest input's tap first) and bias [C], then silu (act = ACT_SILU) or nothing (act < 0); continued from `state` [slots, K - 1,
+    C] (the request's last inputs, oldest first), which the call brings up to date.  -> [T, C] contiguous."""
+    _need_cuda(x, taps, bias, state, token_req, q_start, slots)
+    T, C = x.shape
+    K = taps.shape[0]
+    assert taps.shape == (K, C) and taps.dtype == torch.float32 and taps.is_contiguous()
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == C
+    if K > 1:
+        assert state is not None and state.dtype == x.dtype and state.is_contiguous() and tuple(state.shape[1:]) == (K - 1, C)
+    out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    B = q_start.numel() - 1
+    code = _gated_lib().msgl_causal_conv_act(_ptr(x), _rows_view(x, C, "x"), 0, C, K, _ptr(taps), _ptr(bias), _ptr(state), _ptr(token_req),
+                                             _ptr(q_start), _ptr(slots), _ptr(out), 0 if act == ACT_SILU else -1, T, B, _dt(x), _stream())
+    _check(code, f"causal_conv_act ({K} taps)")
+    if K > 1:
+        global LAUNCHES
+        LAUNCHES += 1
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, *, heads: int, groups: int, state_size: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """State-space recurrence per head over the step's tokens, continued from and written back to `state` [slots, heads, N, P]
+    float32: step = softplus(dt + dt_bias), S <- exp(-exp(a_log) step) S + step B x^T, y = S^T C + skip x, with head h on group
+    h // (heads / groups).  xbc [T, heads * P + 2 groups * N] contiguous = x | B | C; dt [T, heads] a view into packed rows.
+    -> float32 [T, heads * P]."""
+    _need_cuda(xbc, dt, dt_bias, a_log, skip, state, q_start, slots)
+    T = xbc.shape[0]
+    N = state_size
+    P = (xbc.shape[1] - 2 * groups * N) // heads
+    assert xbc.is_contiguous() and xbc.shape[1] == heads * P + 2 * groups * N and dt.dtype == xbc.dtype
+    for w in (dt_bias, a_log, skip):
+        assert w.dtype == torch.float32 and w.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, N, P)
+    y = torch.empty((T, heads * P), dtype=torch.float32, device=xbc.device)
+    B = q_start.numel() - 1
+    code = _gated_lib().msgl_ssm_scan(_ptr(xbc), heads, groups, N, P, _ptr(dt), _rows_view(dt, heads, "dt"), 0, _ptr(dt_bias), _ptr(a_log),
+                                      _ptr(skip), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(y), B, _dt(xbc), _stream())
+    _check(code, f"ssm_scan (state size {N})")
+    return y
+
+
+def gate_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, parts: int, eps: float, out: torch.Tensor,
+                    scale: float = 1.0) -> None:
+    """out = v / rms(v) * weight * scale with v = y * silu(gate) and the root mean square taken over each of `parts` equal parts of
+    the row by itself (the gate comes before the norm).  y float32 [T, N] contiguous; gate and out [T, N] views into packed rows of
+    the activation type; weight float32 [N]."""
+    _need_cuda(y, gate, weight, out)
+    T, N = y.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == N and gate.dtype == out.dtype
+    code = _gated_lib().msgl_gate_group_norm(_ptr(y), N, int(parts), _ptr(weight), float(eps), _ptr(gate), _rows_view(gate, N, "gate"),
+                                             _ptr(out), _rows_view(out, N, "out"), float(scale), T, _dt(out), _stream())
+    _check(code, "gate_group_norm")
+
+
+def unary_act(x: torch.Tensor, act: int, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x) * scale, element by element; act = ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_RELU2 (relu(x)^2) or ACT_RELU."""
+    _need_cuda(x, out)
+    T, N = x.shape
+    if out is None:
+        out = torch.empty((T, N), dtype=x.dtype, device=x.device)
+    assert out.dtype == x.dtype
+    code = _gated_lib().msgl_unary_act(_ptr(x), _rows_view(x, N, "x"), _ptr(out), _rows_view(out, N, "out"), N, int(act), float(scale), T,
+                                       _dt(x), _stream())
+    _check(code, "unary_act")
+    return out
+
+
+def route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], *, n_groups: int, keep: int,
+          top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The experts a token uses and their weights.  Scores s = sigmoid(router h) with float32 sums; the choice goes by s +
+    correction among the experts of the `keep` best of `n_groups` equal groups of neighbouring experts (a group counts by the sum
+    of its two largest choice scores), the `top` largest win; the weights are the winners' s over their sum.
+    h [T, H], router [E, H] -> (int32 [T, top], float32 [T, top])."""
+    _need_cuda(h, router, correction)
+    T, H = h.shape
+    E = router.shape[0]
+    assert router.shape == (E, H) and router.is_contiguous() and router.dtype == h.dtype
+    if correction is not None:
+        assert correction.dtype == torch.float32 and correction.numel() == E
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    code = _gated_lib().msgl_route(_ptr(h), _rows_view(h, H, "h"), _ptr(router), _ptr(correction), H, E, int(n_groups), int(keep),
+                                   int(top), _ptr(idx), _ptr(wts), T, _dt(h), _stream())
+    _check(code, f"route ({E} experts)")
+    return idx, wts
+
+
+def experts_few(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
+                scale: float = 1.0) -> torch.Tensor:
+    """-> float32 [T, H] = scale * sum_k wts[t, k] * down[e] (silu(gate[e] h_t) * (up[e] h_t)), e = idx[t, k], with the chosen
+    experts' rows read straight from the stacked weights gate_up [E, 2, F, H] (an expert's gate, then its up) and down [E, H, F]:
+    for a few tokens."""
+    _need_cuda(h, gate_up, down, idx, wts)
+    T, H = h.shape
+    E, _, F, _ = gate_up.shape
+    top = idx.shape[1]
+    assert gate_up.shape == (E, 2, F, H) and down.shape == (E, H, F)
+    assert gate_up.is_contiguous() and down.is_contiguous() and gate_up.dtype == down.dtype == h.dtype
+    assert idx.dtype == torch.int32 and wts.dtype == torch.float32 and idx.is_contiguous() and wts.is_contiguous()
+    act = torch.empty((T * top, F), dtype=h.dtype, device=h.device)
+    out = torch.empty((T, H), dtype=torch.float32, device=h.device)
+    code = _gated_lib().msgl_experts_few(_ptr(h), _rows_view(h, H, "h"), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(wts), top, H, F,
+                                         _ptr(act), float(scale), _ptr(out), T, _dt(h), _stream())
+    _check(code, "experts_few")
+    global LAUNCHES
+    LAUNCHES += 1
+    return out
+
+
+def expert_order(idx: torch.Tensor, n_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """idx int32 [T, top] -> (counts int32 [E]: pairs per expert; place int32 [T * top]: row of every (token, choice) pair when the
+    pairs are put in the order of their experts, pairs of one expert in their own order)."""
+    _need_cuda(idx)
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    counts = torch.empty(n_experts, dtype=torch.int32, device=idx.device)
+    place = torch.empty(idx.numel(), dtype=torch.int32, device=idx.device)
+    _check(_gated_lib().msgl_expert_order(_ptr(idx), idx.numel(), n_experts, _ptr(counts), _ptr(place), _stream()), "expert_order")
+    global LAUNCHES
+    LAUNCHES += 1
+    return counts, place
+
+
+def expert_gather(h: torch.Tensor, place: torch.Tensor, top: int) -> torch.Tensor:
+    """rows[place[t * top + k]] = h[t]: every token's row once per expert it uses, in expert order."""
+    _need_cuda(h, place)
+    T, H = h.shape
+    rows = torch.empty((T * top, H), dtype=h.dtype, device=h.device)
+    _check(_gated_lib().msgl_expert_gather(_ptr(h), _rows_view(h, H, "h"), _ptr(place), top, H, _ptr(rows), T * top, _dt(h), _stream()),
+           "expert_gather")
+    return rows
+
+
+def expert_combine(y: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """-> float32 [T, H] = scale * sum_k wts[t, k] * y[place[t * top + k]]; y [T * top, H] float32 or bfloat16."""
+    _need_cuda(y, place, wts)
+    T, top = wts.shape
+    H = y.shape[1]
+    assert y.is_contiguous() and y.shape[0] == T * top and wts.dtype == torch.float32 and wts.is_contiguous()
+    _dt(y)
+    out = torch.empty((T, H), dtype=torch.float32, device=y.device)
+    _check(_gated_lib().msgl_expert_combine(_ptr(y), int(y.dtype == torch.float32), _ptr(place), _ptr(wts), top, H, float(scale), _ptr(out),
+                                            T, _stream()), "expert_combine")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
 # the whole decode step in one persistent kernel (csrc/decode_step.cu)
 # ---------------------------------------------------------------------------------------
 # Off unless MSGL_FUSED_DECODE=1: measured on B200 at Qwen3-8B's sizes the one-kernel step takes 4.2 / 5.4 ms at batch 1 / 8

@@ -28,9 +28,11 @@ class PreNormResidualBlock(Block):
             self.position = env.shared(layer_spec.position, lambda: build_part(
                 POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
         self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
-        self.norm_post = build_part(NORMS, "norm", layer_spec.norms["post_mixer"], at("post_mixer"), env)
         self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
-        self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
+        self.norm_post = self.ffn = None
+        if layer_spec.feed_forward is not None:      # a layer without a feed-forward hands its mixer's output on un-added
+            self.norm_post = build_part(NORMS, "norm", layer_spec.norms["post_mixer"], at("post_mixer"), env)
+            self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
 
     def parts(self):
         return [p for p in (self.position, self.norm_in, self.mixer, self.norm_post, self.ffn) if p is not None]
@@ -49,12 +51,16 @@ class PreNormResidualBlock(Block):
         # residual: float32 stream, updated in place; delta: the previous block's output or None
         y = self.norm_in.forward(x=delta, residual=residual, residual_out=residual if delta is not None else None)
         a = self.mixer.forward(y, ctx, cache, writes_cache)
+        if self.ffn is None:
+            return a, residual
         y = self.norm_post.forward(x=a, residual=residual, residual_out=residual)
         return self.ffn.forward(y, ctx), residual
 
     def fused_decode_fields(self):
         """This arrangement is the one the whole-step decode kernel walks (norm, mixer, residual sum, norm, feed-forward,
         residual sum); it takes part if all four parts do."""
+        if self.ffn is None:
+            return None
         parts = {"norm_in": self.norm_in.fused_decode_fields(), "mixer": self.mixer.fused_decode_fields(),
                  "norm_post": self.norm_post.fused_decode_fields(), "ffn": self.ffn.fused_decode_fields()}
         if any(v is None for v in parts.values()):

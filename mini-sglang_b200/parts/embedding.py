@@ -39,6 +39,31 @@ class TokenEmbedding(Part):
         return {"kind": "token_embedding", "weight": self.weight, "V": self.V, "H": self.H}
 
 
+@register_embedding("token_position_embedding")
+class TokenPositionEmbedding(Part):
+    """h = E[ids] * scale + P[position]: a learned vector per place is added to the (scaled) token row, itself unscaled; the sum
+    opens the float32 residual stream.  The table of places bounds the context.
+    params: vocab_size, hidden_size, max_positions, name, position_name, scale (default 1)."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.V, self.H, self.max_positions = int(spec["vocab_size"]), int(spec["hidden_size"]), int(spec["max_positions"])
+        self.tensor_name = spec.get("name") or self.name("weight")
+        self.position_name = spec.get("position_name") or self.name("positions")
+        self.scale = float(spec.get("scale", 1.0))
+        self.weight = self.places = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.tensor_name: TensorDecl((self.V, self.H)), self.position_name: TensorDecl((self.max_positions, self.H))}
+
+    def load(self, src) -> None:
+        self.weight = src.fetch(self.tensor_name).contiguous()
+        self.places = src.fetch(self.position_name).contiguous()
+
+    def forward(self, ids: torch.Tensor, ctx=None) -> torch.Tensor:
+        return ops.embed_positions(ids, ctx.positions, self.weight, self.places, self.scale)
+
+
 @register_head("lm_head")
 class LMHead(Part):
     """logits = h @ W^T in float32 output; W is the embedding matrix itself when tied

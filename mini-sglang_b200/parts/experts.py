@@ -1,0 +1,84 @@
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of small gated feed-forwards of which every token uses `top`.
+
+    Router: scores s = sigmoid(Wr x) with float32 sums; the choice goes by s + correction (a learned number per expert that takes
+    no part in the weights); the experts form `groups` equal groups of neighbours, a group counts by the sum of its two largest
+    choice scores, and only experts of the `keep_groups` best groups can be chosen; the `top` largest choice scores win; their
+    weights are their s over the sum of those (+ 1e-20).  Expert: down_e (silu(gate_e x) * (up_e x)), no biases.  The output is
+    the weighted sum of the chosen experts' outputs, in float32, times `out_scale`.
+
+    A few (token, choice) pairs - and every step that a CUDA graph replays - read the chosen experts' rows straight from the
+    stacked weights (two launches whatever the choice).  Many tokens are put in the order of their experts on the device; the
+    host reads the experts' counts (one small copy) and runs one gate/up product with its activation and one down product per
+    expert that has tokens, on the engine's matrix products; one kernel sums every token's rows with their weights.
+
+    params: hidden_size, intermediate_size, num_experts, top, groups, keep_groups, out_scale,
+            names (router, correction, expert (with {e} for the expert's number), gate, up, down).
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        s = spec
+        self.H, self.F, self.n_exp, self.top = int(s["hidden_size"]), int(s["intermediate_size"]), int(s["num_experts"]), int(s["top"])
+        self.n_groups, self.keep = int(s.get("groups", 1)), int(s.get("keep_groups", s.get("groups", 1)))
+        self.out_scale = float(s.get("out_scale", 1.0))
+        if self.n_exp > ops.ROUTE_MAX_EXPERTS or self.n_groups > ops.ROUTE_MAX_GROUPS:
+            raise ValueError(f"the router kernel takes up to {ops.ROUTE_MAX_EXPERTS} experts in up to {ops.ROUTE_MAX_GROUPS} groups")
+        if self.n_groups < 1 or self.n_exp % self.n_groups or not 1 <= self.keep <= self.n_groups:
+            raise ValueError("the experts must divide into equal groups, of which 1 .. all are kept")
+        if not 1 <= self.top <= self.keep * (self.n_exp // self.n_groups):
+            raise ValueError(f"top = {self.top}: the kept groups hold {self.keep * (self.n_exp // self.n_groups)} experts")
+        names = {"router": "router", "correction": "correction", "expert": "e{e}", "gate": "gate", "up": "up", "down": "down"}
+        names.update(s.get("names") or {})
+        self.names = names
+        self.router = self.correction = self.down = self.gate_up = None
+
+    def _expert(self, e: int, what: str) -> str:
+        return self.name(self.names["expert"].format(e=e) + "." + self.names[what])
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        t = {self.name(self.names["router"]): TensorDecl((self.n_exp, self.H), std=0.5),
+             self.name(self.names["correction"]): TensorDecl((self.n_exp,), kind="vector", std=0.1)}
+        for e in range(self.n_exp):
+            t[self._expert(e, "gate")] = TensorDecl((self.F, self.H))
+            t[self._expert(e, "up")] = TensorDecl((self.F, self.H))
+            t[self._expert(e, "down")] = TensorDecl((self.H, self.F))
+        return t
+
+    def load(self, src) -> None:
+        f = src.fetch
+        self.router = f(self.name(self.names["router"])).contiguous()
+        self.correction = f(self.name(self.names["correction"])).float().contiguous()
+        # [E, 2, F, H]: an expert's gate and up side by side are the packed matrix of the fused product + activation
+        self.gate_up = torch.stack([torch.stack((f(self._expert(e, "gate")), f(self._expert(e, "up")))) for e in range(self.n_exp)]).contiguous()
+        self.down = torch.stack([f(self._expert(e, "down")) for e in range(self.n_exp)]).contiguous()
+
+    def forward(self, x, ctx):
+        idx, wts = ops.route(x, self.router, self.correction, n_groups=self.n_groups, keep=self.keep, top=self.top)
+        T = x.shape[0]
+        if ctx.uniform_decode or T * self.top <= ops.EXPERTS_FEW_PAIRS:
+            return ops.experts_few(x, self.gate_up, self.down, idx, wts, self.out_scale)
+        counts, place = ops.expert_order(idx, self.n_exp)
+        rows = ops.expert_gather(x, place, self.top)
+        y = torch.empty((T * self.top, self.H), dtype=torch.float32, device=x.device)
+        at = 0
+        for e, n in enumerate(counts.tolist()):          # the one read of device data on the host: the experts' row counts
+            if n:
+                a = ops.linear_swiglu(rows[at:at + n], self.gate_up[e].view(2 * self.F, self.H))
+                y[at:at + n] = ops.linear(a, self.down[e], out_dtype=torch.float32)
+                at += n
+        return ops.expert_combine(y, place, wts, self.out_scale)

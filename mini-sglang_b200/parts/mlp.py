@@ -81,3 +81,34 @@ class GatedMLP(FeedForward, Projected):
         if self.act == ops.ACT_SILU:        # product and activation in one kernel where the engine has it (few rows; many rows in bfloat16)
             return ops.linear(ops.linear_swiglu(x, self.gate_up), self.down)
         return self.forward_projected(x, ctx)
+
+
+UNARY_ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu_tanh": ops.ACT_GELU_TANH, "relu2": ops.ACT_RELU2, "relu": ops.ACT_RELU}
+
+
+@register_feed_forward("plain_mlp")
+class PlainMLP(FeedForward):
+    """down(act(up(x))), dense, no gate, no biases; act = "relu2" (the square of relu), "relu", "silu" or "gelu_tanh".  The result
+    is float32, times `out_scale` (applied to the activation, before the second product).
+    params: hidden_size, intermediate_size, activation, out_scale, names (up, down)."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.H, self.I = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        act = spec.get("activation", "relu2")
+        if act not in UNARY_ACTIVATIONS:
+            raise ValueError(f"unknown activation {act!r}; known: " + ", ".join(sorted(UNARY_ACTIVATIONS)))
+        self.act, self.out_scale = UNARY_ACTIVATIONS[act], float(spec.get("out_scale", 1.0))
+        names = spec.get("names") or {}
+        self.n_up, self.n_down = self.name(names.get("up", "up_proj.weight")), self.name(names.get("down", "down_proj.weight"))
+        self.up = self.down = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.n_up: TensorDecl((self.I, self.H)), self.n_down: TensorDecl((self.H, self.I))}
+
+    def load(self, src) -> None:
+        self.up, self.down = src.fetch(self.n_up).contiguous(), src.fetch(self.n_down).contiguous()
+
+    def forward(self, x, ctx):
+        u = ops.linear(x, self.up)
+        return ops.linear(ops.unary_act(u, self.act, self.out_scale, out=u), self.down, out_dtype=torch.float32)
