@@ -575,12 +575,37 @@ def nametar_config(size, layers, vocab, window=1024):
             "embedding": {"scale": float(s["width"]) ** 0.5}, "layers": [kinds[i % 4] for i in range(layers)]}
 
 
+def pepevik_config(size, layers, vocab):
+    """A Pepevik model with the given layer sizes.  The sigmoid attention has the heads of the Qwen3 layer (key and value size of
+    the head) beside a minGRU as wide as the model; the state-space mixer has twice the width in heads of 64 with a state of 128,
+    eight groups, four taps; the dense feed-forward has the layer's width, the routed one 32 experts in 4 groups (2 kept) of which
+    a token uses 4, each a quarter as wide, so that a token meets as many feed-forward weights either way.  Kinds of layers in
+    turn: pair + dense, state space + routed, pair + routed, state space + dense; every layer has tensors of its own."""
+    s = COMPARE_SIZES[size]
+    pair = {"type": "parallel",
+            "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                               "scale": s["dim"] ** -0.5, "q_temp": {"coef": 0.5, "every": 1024}},
+                      "right": {"width": s["width"]}}}
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * s["width"] // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"] // 4}, "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    kinds = [dict(pair, mlp=dense), dict(ssm, mlp=moe), dict(pair, mlp=moe), dict(ssm, mlp=dense)]
+    return {"architecture": "Pepevik", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": float(s["width"]) ** 0.5}, "max_positions": 8192, "layers": [kinds[i % 4] for i in range(layers)]}
+
+
+def workload_pepevik(args):
+    """As --workload vekurax_compare, with a Pepevik model (`pepevik_config`) beside the Vekurax model of equal sizes (the engine's
+    other design whose mixer is an attention and a recurrence side by side)."""
+    return workload_vekurax(args, name="pepevik", config=pepevik_config, beside="vekurax")
+
+
 def workload_nametar(args):
     """As --workload vekurax_compare, with a Nametar model (`nametar_config`) beside the Qwen3 model of equal sizes."""
     return workload_vekurax(args, name="nametar", config=nametar_config)
 
 
-def workload_vekurax(args, name="vekurax", config=None):
+def workload_vekurax(args, name="vekurax", config=None, beside="qwen3"):
     """Prefill (one 2,048-token prompt a step) and decode (--batch requests at --context tokens, one token each a step through
     the CUDA graph) of a Vekurax model and of a Qwen3 model with the same width, heads, feed-forward width, vocabulary and number
     of layers (--layers, default 4; random weights), device-timed, with the mean time of every kernel of a step."""
@@ -606,7 +631,7 @@ def workload_vekurax(args, name="vekurax", config=None):
                     num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=V,
                     tie_word_embeddings=True, max_position_embeddings=CTX + 4096)
         res = {}
-        for arch, cfg in ((name, config(size, L, V)), ("qwen3", qwen)):
+        for arch, cfg in ((name, config(size, L, V)), (beside, qwen if beside == "qwen3" else vekurax_config(size, L, V))):
             tmp = tempfile.mkdtemp(prefix="msgl_bench_")
             with open(os.path.join(tmp, "config.json"), "w") as f:
                 json.dump(cfg, f)
@@ -681,9 +706,9 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
-    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare", "pepevik_compare"],
                     help="headline: the line the contract names; the others: further workloads, one JSON line each")
-    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
+    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare / pepevik_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")
     ap.add_argument("--lengths", default=None,
@@ -707,6 +732,8 @@ def main():
         return workload_vekurax(args)
     if args.workload == "nametar_compare":
         return workload_nametar(args)
+    if args.workload == "pepevik_compare":
+        return workload_pepevik(args)
 
     import torch
 

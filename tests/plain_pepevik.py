@@ -171,7 +171,7 @@ def forward_sequence(config: dict, w: Dict[str, torch.Tensor], tokens: List[int]
     eps, m = config["norm"]["eps"], config.get("residual_mult", 1.0)
     if len(tokens) > config["max_positions"]:
         raise ValueError("more tokens than the model has places")
-    x = embed(tokens, w, config["embedding"]["scale"])
+    x = embed(tokens, w, (config.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(config["layers"]):
         o = i
         while config["layers"][o].get("weights_of") is not None:
@@ -193,3 +193,13 @@ def forward_sequence(config: dict, w: Dict[str, torch.Tensor], tokens: List[int]
         if streams is not None:
             streams.append(x.clone())
     return dynamic_tanh(x, w, "final.norm") @ w["head"].T
+
+
+def greedy_generate(config: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    toks, out = list(prompt), []
+    for _ in range(n):
+        with torch.no_grad():
+            t = int(forward_sequence(config, w, toks)[-1].argmax())
+        out.append(t)
+        toks.append(t)
+    return out

@@ -1,0 +1,705 @@
+"""The Pepevik parts and the whole model in the engine against the plain implementation (tests/plain_pepevik.py).
+
+Kernels one by one; the sigmoid attention with inputs made so that a fault shows (one key whose weight is nearly 1 among
+hundreds whose weights are nearly 0: far away, on the first token, at page borders, in the future); the recurrences in
+portions and shared steps with state rows that are used again; then the model through the step function: whole prompts,
+token by token, in portions down to two tokens, mixed batches on a pool so small that pages and request slots are used
+again, long decoding, greedy generation through the engine's entry point, and the trace replay program.
+"""
+
+import functools
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_pepevik as pp
+from helpers import assert_row_close, play
+from tiny_models import random_tokens, write_model_dir
+from tiny_pepevik import CONFIGS_P, make_weights
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SEED = {"PA": 3, "PB": 4, "PC": 5}
+PAGE = {"PA": 4, "PB": 1, "PC": 16}
+_tmp = tempfile.TemporaryDirectory(prefix="msgl_pepevik_")
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+F64 = torch.float64
+
+
+@functools.lru_cache(None)
+def weights(name):
+    return make_weights(CONFIGS_P[name], SEED[name])
+
+
+@functools.lru_cache(None)
+def model_dir(name):
+    return write_model_dir(os.path.join(_tmp.name, name), CONFIGS_P[name], weights(name))
+
+
+@functools.lru_cache(None)
+def plain(name, tokens):
+    with torch.no_grad():
+        return pp.forward_sequence(CONFIGS_P[name], weights(name), list(tokens)).float()
+
+
+def runner(name, dtype, num_pages, max_reqs=4, page_size=None, graphs=True):
+    from mini_sglang_b200.engine.step import ModelRunner
+    return ModelRunner.from_model_dir(model_dir(name), dtype=dtype, page_size=page_size or PAGE[name], num_pages=num_pages,
+                                      max_reqs=max_reqs, max_context_len=512, use_cuda_graph=graphs)
+
+
+# bfloat16: projections, cached keys and values and the activations between kernels are rounded to 8 mantissa bits; scores,
+# sigmoids, norms, gates, decays, states and the stream are float32 in both precisions.  The mixers' outputs are normed to unit
+# size before they are added, so the rounding of a mixer's last product reaches the stream undamped; the noise of the logits stays
+# near 1 % of a row's rms at these widths.  The bound is 3 %; the faults it is meant to catch move the rows by 3.5 % or more
+# (tests/test_pepevik_cpu.py), and the float32 run of the same schedule holds the logic to 1e-4.
+BF16_RMS_FRACTION_P = 0.03
+
+
+def row_close(row, want, dtype, bound=BF16_RMS_FRACTION_P):
+    if dtype == "float32":
+        return assert_row_close(row, want, dtype)
+    row, want = row.float(), want.float()
+    assert torch.isfinite(row).all(), "logits are not finite"
+    err = row - want
+    scale = want.pow(2).mean().sqrt().item()
+    rms, worst = err.pow(2).mean().sqrt().item(), err.abs().max().item()
+    assert rms <= bound * scale, f"rms error {rms:.4g} is {rms / scale:.2%} of the row's rms {scale:.4g}"
+    assert worst <= 6.0 * bound * scale, f"largest error {worst:.4g} is {worst / scale:.2%} of the row's rms {scale:.4g}"
+
+
+def compare(name, dtype, got, seqs, ref=None, bound=BF16_RMS_FRACTION_P):
+    """Every row against the plain implementation.  bfloat16: rounding noise has outliers (a token whose router scores are a
+    close call, a row whose sums nearly cancel before a norm), so one row in fifty (at least one) may pass the bound, none by more
+    than two and a half times; a fault of the cache or of a state moves every row behind it by more than that."""
+    assert got
+    over = []
+    for (rid, pos), row in sorted(got.items()):
+        want = ref[rid][pos] if ref is not None else plain(name, tuple(seqs[rid]))[pos]
+        try:
+            row_close(row, want, dtype, bound)
+        except AssertionError as e:
+            if dtype == "bfloat16" and torch.isfinite(row).all():
+                try:
+                    row_close(row, want, dtype, 2.5 * bound)
+                    over.append((rid, pos))
+                    continue
+                except AssertionError:
+                    pass
+            raise AssertionError(f"request {rid!r} position {pos} ({dtype}, {name}): {e}") from None
+    assert len(over) <= max(1, len(got) // 50), f"{len(over)} of {len(got)} rows beyond the bound ({dtype}, {name}): {over[:8]}"
+
+
+def poison(r):
+    """Whatever a page or a state row held before must not be read: fill the caches with NaN (state rows are zeroed when a
+    request is opened).  Page 0 and state row 0 are never handed out; they take the rows of padded batch rows and hold finite
+    numbers at all times."""
+    for k, v in r.storage.kv.values():
+        k[1:].fill_(float("nan"))
+        v[1:].fill_(float("nan"))
+    for s in r.storage.state.values():
+        s[1:].fill_(float("nan"))
+
+
+def tol_of(dtype, f32=1e-5, bf16=2e-2):
+    return dict(rtol=f32, atol=f32) if dtype == "float32" else dict(rtol=bf16, atol=bf16)
+
+
+def i32(v):
+    return torch.tensor(v, dtype=torch.int32, device="cuda")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# kernels alone
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_with_places(dtype):
+    from mini_sglang_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    table, places = torch.randn(23, 70, generator=g).to(DT[dtype]), torch.randn(40, 70, generator=g).to(DT[dtype])
+    ids, pos = [5, 0, 22, 5, 11], [0, 39, 7, 1, 0]
+    got = ops.embed_positions(i32(ids), i32(pos), table.cuda(), places.cuda(), 12.5).cpu()
+    torch.testing.assert_close(got, table.float()[ids] * 12.5 + places.float()[pos], rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H", [48, 256, 1000, 4096])
+def test_two_normed_outputs_joined(dtype, H):
+    from mini_sglang_b200 import ops
+    g = torch.Generator().manual_seed(H)
+    wa, wb = 1 + 0.1 * torch.randn(H, generator=g), 1 + 0.1 * torch.randn(H, generator=g)
+    for in_dt in {DT[dtype], torch.float32}:
+        a, b = (5 * torch.randn(6, H, generator=g)).to(in_dt), (0.01 * torch.randn(6, H, generator=g)).to(in_dt)
+        got = ops.pair_norm(a.cuda(), b.cuda(), wa.cuda(), wb.cuda(), 1e-5, 0.35).cpu()
+        want = 0.35 * (pp.rms_unit(a.double(), 1e-5) * wa + pp.rms_unit(b.double(), 1e-5) * wb)
+        torch.testing.assert_close(got, want.float(), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_activations_and_gated_group_norm(dtype):
+    from mini_sglang_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    dt = DT[dtype]
+    x = (3 * torch.randn(5, 77, generator=g)).to(dt)
+    packed = torch.cat((torch.zeros(5, 3, dtype=dt), x, torch.zeros(5, 2, dtype=dt)), dim=1).cuda()
+    got = ops.unary_act(packed[:, 3:80], ops.ACT_RELU2, 0.7).float().cpu()
+    torch.testing.assert_close(got, (torch.relu(x.float()) ** 2 * 0.7).to(dt).float(), **tol_of(dtype, 1e-6, 1e-2))
+    for N, parts in ((96, 2), (40, 1), (48, 6), (192, 4), (520, 5)):
+        y = 2 * torch.randn(7, N, generator=g)
+        z = torch.randn(7, N + 9, generator=g).to(dt)
+        w = 1 + 0.1 * torch.randn(N, generator=g)
+        out = torch.full((7, N + 4), float("nan"), dtype=dt, device="cuda")
+        ops.gate_group_norm(y.cuda(), z.cuda()[:, 5:5 + N], w.cuda(), parts, 1e-5, out[:, 4:], 0.5)
+        v = y.double() * pp.silu(z[:, 5:5 + N].double())
+        want = (pp.rms_unit(v.view(7, parts, N // parts), 1e-5).reshape(7, N) * w * 0.5).float()
+        torch.testing.assert_close(out[:, 4:].float().cpu(), want, **tol_of(dtype, 1e-5, 1e-2))
+        assert torch.isnan(out[:, :4]).all()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("geo", [dict(H=6, G=3, d=24, dv=40, coef=0.5, every=8), dict(H=1, G=1, d=36, dv=8, coef=0.0, every=1),
+                                 dict(H=16, G=1, d=96, dv=64, coef=1.5, every=1), dict(H=4, G=4, d=130, dv=33, coef=0.25, every=3)])
+def test_head_norms_query_factor_and_cache_rows(dtype, geo):
+    """q and k normed per head with one weight for all heads, q times the factor of its place, k and v rows at the token slots
+    the step names (pages in any order), heads of different sizes for keys and values."""
+    from mini_sglang_b200 import ops
+    H, G, d, dv = geo["H"], geo["G"], geo["d"], geo["dv"]
+    g = torch.Generator().manual_seed(d)
+    dt, T, P = DT[dtype], 9, 4
+    proj = (2 * torch.randn(T, H * d + G * d + G * dv + 3, generator=g)).to(dt)
+    wq, wk = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    pos = [0, 1, 6, 7, 8, 15, 16, 23, 300]
+    loc = [5, 4, 17, 0 + 2 * P, 3, 30, 31, 9, 12]
+    kc = torch.full((8, G, P, d), float("nan"), dtype=dt, device="cuda")
+    vc = torch.full((8, G, P, dv), float("nan"), dtype=dt, device="cuda")
+    pc = proj.cuda()
+    a, b, c = H * d, H * d + G * d, H * d + G * d + G * dv
+    q = ops.headnorm_kvwrite(pc[:, :a], pc[:, a:b], pc[:, b:c], n_q=H, n_kv=G, q_weight=wq.cuda(), k_weight=wk.cuda(), eps=1e-5,
+                             temp_coef=geo["coef"], temp_every=geo["every"], positions=i32(pos), out_loc=i32(loc), k_cache=kc, v_cache=vc,
+                             page_size=P)
+    f = proj.double()
+    factor = torch.tensor([1 + geo["coef"] * math.log((p + 1) // geo["every"] + 1) for p in pos], dtype=F64)
+    want_q = pp.rms_unit(f[:, :a].view(T, H, d), 1e-5) * wq * factor[:, None, None]
+    want_k = pp.rms_unit(f[:, a:b].view(T, G, d), 1e-5) * wk
+    torch.testing.assert_close(q.float().cpu(), want_q.float(), **tol_of(dtype, 1e-5, 1e-2))
+    for t, l in enumerate(loc):
+        torch.testing.assert_close(kc[l // P, :, l % P].float().cpu(), want_k[t].float(), **tol_of(dtype, 1e-5, 1e-2))
+        torch.testing.assert_close(vc[l // P, :, l % P].float().cpu(), f[t, b:c].view(G, dv).float(), rtol=0, atol=0)
+    assert int(torch.isnan(kc[:, 0, :, 0]).sum()) == 8 * P - T
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# sigmoid attention: every key stands by itself, so ONE key is made to take a weight of nearly 1 among keys of weight nearly 0
+# ---------------------------------------------------------------------------------------------------------------------
+def _sigmoid_case(dtype, *, H, G, d, dv, P, ctx, n_new, spike, seed, wide_table=0, L_bias=None):
+    """`ctx` tokens lie in the cache, `n_new` more are the step's; the key at absolute position `spike` (negative: none) points
+    the way every query points, all other scores sit near -14.  Returns the expected output [n_new, H, dv] (float64 sums over
+    the numbers the kernel reads).  L_bias: the bias table's length (distances beyond it take its last entry)."""
+    from mini_sglang_b200 import ops
+    g = torch.Generator().manual_seed(seed)
+    dt = DT[dtype]
+    L = ctx + n_new
+    L_bias = L_bias or L + 3
+    way = torch.randn(d, generator=g)
+    way = way / way.norm()
+    q = (0.05 * torch.randn(n_new, H, d, generator=g) + 6.0 * way).to(dt)
+    k = (0.05 * torch.randn(L, G, d, generator=g)).to(dt)
+    v = torch.randn(L, G, dv, generator=g).to(dt)
+    tall = (7.0 + torch.randn(G, dv, generator=g)).to(dt)
+    if spike >= 0:
+        k[spike] = (6.0 * way).to(dt)                     # q . k = 36 there: whatever the bias below takes off, the weight is nearly 1
+        v[spike] = tall
+    r1, r2, pb = 0.5 + torch.rand(H, generator=g), 0.1 + torch.rand(H, generator=g), -14.0 + torch.randn(H, generator=g)
+    dist = torch.arange(L_bias, dtype=F64)
+    bias = (pb.double()[:, None] - r1.double()[:, None] * torch.log1p(r2.double()[:, None] * dist[None, :])).float().contiguous()
+    qd, kd, vd = q.double(), k.double(), v.double()
+    want = torch.zeros(n_new, H, dv, dtype=F64)
+    for t in range(n_new):
+        i = ctx + t
+        for h in range(H):
+            s = kd[:i + 1, h // (H // G)] @ qd[t, h] + bias[h].double()[(i - torch.arange(i + 1)).clamp(max=L_bias - 1)]
+            want[t, h] = torch.sigmoid(s) @ vd[:i + 1, h // (H // G)]
+    n_pages = -(-L // P)
+    perm = torch.randperm(n_pages + 3, generator=g)[:n_pages] + 1
+    kc = torch.full((n_pages + 4, G, P, d), float("nan"), dtype=dt)
+    vc = torch.full((n_pages + 4, G, P, dv), float("nan"), dtype=dt)
+    for p in range(L):
+        kc[perm[p // P], :, p % P] = k[p]
+        vc[perm[p // P], :, p % P] = v[p]
+    table = torch.zeros(1, n_pages + wide_table, dtype=torch.int32)         # columns past the request's pages name page 0
+    table[0, :n_pages] = perm.to(torch.int32)
+    kc[0], vc[0] = 0, 0
+    out = torch.full((n_new, H * dv + 8), float("nan"), dtype=dt).cuda()
+    ops.sigmoid_attention(q.cuda(), out[:, 8:], kc.cuda(), vc.cuda(), q_start=i32([0, n_new]), kv_len=i32([L]), block_table=table.cuda(),
+                          n_kv=G, page_size=P, scale=1.0, bias=bias.cuda(), q_lens=None if n_new == 1 else [n_new])
+    got = out[:, 8:].float().cpu().view(n_new, H, dv)
+    assert torch.isfinite(got).all() and torch.isnan(out[:, :8]).all()
+    torch.testing.assert_close(got, want.float(), **tol_of(dtype, 2e-5, 4e-2))
+    return want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_new", [1, 2, 13])
+def test_sigmoid_attention_sees_every_earlier_key_and_no_later_one(dtype, n_new):
+    geo = dict(H=6, G=3, d=24, dv=40, P=4, ctx=300, n_new=n_new, seed=21)
+    last = {}
+    for name, spike in (("none", -1), ("first", 0), ("second", 1), ("far", 37), ("page end", 3), ("page start", 4), ("chunk edge", 31),
+                        ("next chunk", 32), ("just before", 299), ("own", 300 + n_new - 1), ("piece edge", 255), ("next piece", 256)):
+        last[name] = _sigmoid_case(dtype, spike=spike, **geo)[-1]
+    for name in last:
+        if name != "none":           # seeing or not seeing that one key changes the output grossly, however far away it is
+            assert (last[name] - last["none"]).abs().min() > 1.0, name
+    if n_new > 1:
+        # a key of the same portion that comes AFTER a query is not seen by it, and is seen by the later ones
+        w = _sigmoid_case(dtype, spike=300 + n_new - 1, **geo)
+        none = _sigmoid_case(dtype, spike=-1, **geo)
+        assert (w[:-1] - none[:-1]).abs().max() < 1e-9 and (w[-1] - none[-1]).abs().min() > 1.0
+        w = _sigmoid_case(dtype, spike=300, **geo)
+        assert (w - none).abs().amin(dim=(1, 2)).min() > 1.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sigmoid_attention_other_geometries(dtype):
+    # the first tokens of a sequence: nothing cached, one and two tokens, a long portion
+    _sigmoid_case(dtype, H=2, G=1, d=40, dv=24, P=4, ctx=0, n_new=1, spike=0, seed=1)
+    _sigmoid_case(dtype, H=2, G=1, d=40, dv=24, P=4, ctx=0, n_new=2, spike=1, seed=2)
+    _sigmoid_case(dtype, H=2, G=2, d=160, dv=72, P=8, ctx=0, n_new=70, spike=33, seed=3)
+    # the second token decoded; sixteen heads on one kv head (two blocks of heads), value rows longer than key rows
+    _sigmoid_case(dtype, H=4, G=2, d=32, dv=32, P=4, ctx=1, n_new=1, spike=0, seed=4)
+    _sigmoid_case(dtype, H=16, G=1, d=64, dv=96, P=16, ctx=70, n_new=9, spike=40, seed=5)
+    _sigmoid_case(dtype, H=16, G=1, d=96, dv=64, P=16, ctx=500, n_new=1, spike=17, seed=6)
+    # pages of one token; one head; head sizes that are no multiple of anything
+    _sigmoid_case(dtype, H=1, G=1, d=36, dv=9, P=1, ctx=40, n_new=5, spike=3, seed=7)
+    _sigmoid_case(dtype, H=3, G=3, d=13, dv=130, P=2, ctx=90, n_new=3, spike=64, seed=8)
+    # a decoded token whose keys are cut into pieces: the far key in the first, a middle and the last piece, the block table wider
+    # than the request needs (pieces without keys), the context ending on a piece's edge and one behind it
+    for ctx, spike in ((1000, 5), (1000, 600), (1000, 999), (511, 255), (512, 512), (767, 300)):
+        _sigmoid_case(dtype, H=8, G=2, d=96, dv=96, P=16, ctx=ctx, n_new=1, spike=spike, seed=9, wide_table=40)
+    # head size 128 in a long portion behind a cached context (the serving shape)
+    _sigmoid_case(dtype, H=8, G=2, d=128, dv=128, P=16, ctx=200, n_new=150, spike=120, seed=10)
+    # distances beyond the bias table take its last entry
+    _sigmoid_case(dtype, H=2, G=1, d=16, dv=16, P=4, ctx=50, n_new=4, spike=2, seed=11, L_bias=20)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# the recurrences: portions, shared steps, state rows used again
+# ---------------------------------------------------------------------------------------------------------------------
+def _shared_steps(lens, cuts, order, run):
+    """Feeds every request r (lens[r] tokens, cut as cuts[r]) through `run(reqs, starts, ns)` in shared steps; -> {r: rows}."""
+    at = {r: 0 for r in lens}
+    got = {r: [] for r in lens}
+    cuts = {r: list(c) for r, c in cuts.items()}
+    while any(cuts.values()):
+        reqs = [r for r in order if cuts[r]]
+        ns = [cuts[r].pop(0) for r in reqs]
+        o = run(reqs, [at[r] for r in reqs], ns)
+        k = 0
+        for r, n in zip(reqs, ns):
+            got[r].append(o[k:k + n].float().cpu())
+            k += n
+            at[r] += n
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("W", [5, 72, 300])
+def test_min_gru_in_portions_and_batches(dtype, W):
+    """Three requests with states of their own in shared steps (ninety single tokens among them), gates from nearly closed to
+    nearly open, candidates on both sides of zero; a fourth request then takes a state row that was used before."""
+    from mini_sglang_b200 import ops
+    g = torch.Generator().manual_seed(W)
+    dt = DT[dtype]
+    lens = {0: 90, 1: 37, 2: 64}
+    u = {r: (3 * torch.randn(n, 3 * W + 5, generator=g)).to(dt) for r, n in lens.items()}
+    zb, xb = 2 * torch.randn(W, generator=g), torch.randn(W, generator=g)
+    state = torch.full((5, W), float("nan")).cuda()
+    state[1:4].zero_()
+
+    def run(reqs, starts, ns):
+        x = torch.cat([u[r][a:a + n] for r, a, n in zip(reqs, starts, ns)]).cuda()
+        out = torch.full((x.shape[0], W + 3), float("nan"), dtype=dt).cuda()
+        ops.mingru(x[:, 2:2 + W], x[:, 2 + W:2 + 2 * W], x[:, 2 + 2 * W:2 + 3 * W], zb.cuda(), xb.cuda(), state=state,
+                   q_start=i32(np.concatenate(([0], np.cumsum(ns))).tolist()), slots=i32([r + 1 for r in reqs]), out=out[:, 3:], scale=0.7)
+        assert torch.isnan(out[:, :3]).all()
+        return out[:, 3:]
+
+    def want(x):
+        f = x.double()
+        z, a, gate = torch.sigmoid(f[:, 2:2 + W] + zb), f[:, 2 + W:2 + 2 * W] + xb, f[:, 2 + 2 * W:2 + 3 * W]
+        c = torch.where(a >= 0, a + 0.5, torch.sigmoid(a))
+        S, rows = torch.zeros(W, dtype=F64), []
+        for t in range(x.shape[0]):
+            S = (1 - z[t]) * S + z[t] * c[t]
+            rows.append(S * pp.silu(gate[t]) * 0.7)
+        return torch.stack(rows).float()
+
+    got = _shared_steps(lens, {0: [1] * 90, 1: [30, 2, 2, 3], 2: [5, 40, 1, 1, 17]}, (2, 0, 1), run)
+    for r in lens:
+        torch.testing.assert_close(got[r], want(u[r]), **tol_of(dtype, 2e-5, 2e-2))
+    state[2].zero_()                                       # the row of request 1, handed to a new request
+    lens2 = {1: 21}
+    u[1] = (3 * torch.randn(21, 3 * W + 5, generator=g)).to(dt)
+    got = _shared_steps(lens2, {1: [2, 19]}, (1,), run)
+    torch.testing.assert_close(got[1], want(u[1]), **tol_of(dtype, 2e-5, 2e-2))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("geo", [dict(heads=4, P=12, N=16, groups=2, K=3), dict(heads=1, P=20, N=8, groups=1, K=1),
+                                 dict(heads=6, P=8, N=40, groups=3, K=2), dict(heads=2, P=40, N=24, groups=1, K=4),
+                                 dict(heads=8, P=64, N=128, groups=8, K=4)])
+def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo):
+    """The short convolution continued from a request's last inputs (portions shorter than the taps among them) and the scan
+    continued from its state, three requests in shared steps, against the recurrence written out; steps from tiny to large."""
+    from mini_sglang_b200 import ops
+    heads, P, N, groups, K = geo["heads"], geo["P"], geo["N"], geo["groups"], geo["K"]
+    g = torch.Generator().manual_seed(N + K)
+    dt = DT[dtype]
+    inner, gn = heads * P, groups * N
+    C = inner + 2 * gn
+    lens = {0: 70, 1: 37, 2: 64}
+    u = {r: torch.randn(n, 3 + C + heads, generator=g).to(dt) for r, n in lens.items()}
+    for r in u:
+        u[r][:, 3 + C:] *= 3.0                          # step inputs: softplus from nearly 0 to several
+    taps, cb = 0.5 * torch.randn(C, K, generator=g), 0.1 * torch.randn(C, generator=g)
+    dtb, alog, skip = 0.5 * torch.randn(heads, generator=g), 0.5 * torch.randn(heads, generator=g), 1 + 0.1 * torch.randn(heads, generator=g)
+    conv_state = torch.full((5, max(K - 1, 0), C), float("nan"), dtype=dt).cuda()
+    ssm_state = torch.full((5, heads, N, P), float("nan")).cuda()
+    conv_state[1:4].zero_()
+    ssm_state[1:4].zero_()
+    tw = taps.t().contiguous().cuda()
+
+    def run(reqs, starts, ns):
+        x = torch.cat([u[r][a:a + n] for r, a, n in zip(reqs, starts, ns)]).cuda()
+        q_start = i32(np.concatenate(([0], np.cumsum(ns))).tolist())
+        slots = i32([r + 1 for r in reqs])
+        token_req = i32([i for i, n in enumerate(ns) for _ in range(n)])
+        xbc = ops.causal_conv_act(x[:, 3:3 + C], tw, cb.cuda(), state=conv_state if K > 1 else None, token_req=token_req,
+                                  q_start=q_start, slots=slots)
+        return ops.ssm_scan(xbc, x[:, 3 + C:], heads=heads, groups=groups, state_size=N, dt_bias=dtb.cuda(), a_log=alog.cuda(),
+                            skip=skip.cuda(), state=ssm_state, q_start=q_start, slots=slots)
+
+    def want(x):
+        f = x.double()
+        n = f.shape[0]
+        xbc = pp.silu(pp.causal_conv(f[:, 3:3 + C], taps.double(), cb.double())).to(dt).double()      # the scan reads rounded rows
+        xs, B, Cc = xbc[:, :inner].view(n, heads, P), xbc[:, inner:inner + gn].view(n, groups, N), xbc[:, inner + gn:].view(n, groups, N)
+        step = torch.nn.functional.softplus(f[:, 3 + C:] + dtb, threshold=1e9)
+        S, rows = torch.zeros(heads, N, P, dtype=F64), []
+        for t in range(n):
+            y = torch.zeros(heads, P, dtype=F64)
+            for h in range(heads):
+                gi = h // (heads // groups)
+                S[h] = torch.exp(-torch.exp(alog[h].double()) * step[t, h]) * S[h] + step[t, h] * B[t, gi][:, None] * xs[t, h][None, :]
+                y[h] = S[h].T @ Cc[t, gi] + skip[h] * xs[t, h]
+            rows.append(y.reshape(-1))
+        return torch.stack(rows).float()
+
+    got = _shared_steps(lens, {0: [1] * 70, 1: [30, 2, 2, 3], 2: [1, 1, 2, 43, 1, 16]}, (2, 0, 1), run)
+    for r in lens:
+        torch.testing.assert_close(got[r], want(u[r]), **tol_of(dtype, 5e-5, 3e-2))
+    conv_state[1].zero_()
+    ssm_state[1].zero_()                                   # request 0's rows, handed to a new request
+    u[0] = torch.randn(9, 3 + C + heads, generator=g).to(dt)
+    got = _shared_steps({0: 9}, {0: [2, 1, 6]}, (0,), run)
+    torch.testing.assert_close(got[0], want(u[0]), **tol_of(dtype, 5e-5, 3e-2))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# router and experts
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("geo", [dict(E=8, count=4, keep=2, top=3), dict(E=5, count=5, keep=2, top=1), dict(E=6, count=1, keep=1, top=2),
+                                 dict(E=16, count=4, keep=2, top=4), dict(E=64, count=8, keep=3, top=6), dict(E=12, count=2, keep=1, top=6)])
+def test_router_choice_and_weights(dtype, geo):
+    from mini_sglang_b200 import ops
+    E, H, T = geo["E"], 40, 50
+    g = torch.Generator().manual_seed(E)
+    dt = DT[dtype]
+    h = torch.randn(T, H, generator=g).to(dt)
+    router = (3 * torch.randn(E, H, generator=g) / math.sqrt(H)).to(dt)
+    corr = torch.randn(E, generator=g)
+    corr[: E // 2] -= 3.0                                  # choice scores of both signs: a group that is out counts as minus infinity
+    r = {"experts": E, "top": geo["top"], "groups": {"count": geo["count"], "keep": geo["keep"]}}
+    idx_w, wts_w = pp.route(h.float(), {"f.router": router.float(), "f.correction": corr}, "f", r)
+    idx, wts = ops.route(h.cuda(), router.cuda(), corr.cuda(), n_groups=geo["count"], keep=geo["keep"], top=geo["top"])
+    idx, wts = idx.cpu().long(), wts.cpu()
+    s = torch.sigmoid(h.double() @ router.double().T)
+    margin_ok = 0
+    for t in range(T):
+        if sorted(idx[t].tolist()) != sorted(idx_w[t].tolist()):
+            continue                                       # a close call between two experts may fall either way; counted below
+        margin_ok += 1
+        by = dict(zip(idx[t].tolist(), wts[t].tolist()))
+        tot = sum(float(s[t, e]) for e in by)
+        for e, a in by.items():
+            assert abs(a - float(s[t, e]) / tot) < 1e-5
+    assert margin_ok >= T - 1, f"{T - margin_ok} of {T} tokens chose other experts than the plain router"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T", [1, 7, 150])
+def test_experts_both_ways(dtype, T):
+    """The chosen experts' products straight from the stacked weights (few tokens, and every decode step) and in expert order
+    (many tokens) against the sum written out; experts that no token chose, tokens that all choose the same expert."""
+    from mini_sglang_b200 import ops
+    E, H, F, top = 6, 48, 24, 2
+    g = torch.Generator().manual_seed(T)
+    dt = DT[dtype]
+    h = torch.randn(T, H, generator=g).to(dt)
+    gu = (torch.randn(E, 2, F, H, generator=g) / math.sqrt(H)).to(dt)
+    dn = (torch.randn(E, H, F, generator=g) / math.sqrt(F)).to(dt)
+    idx = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(T)]).to(torch.int32)      # expert 5 is never chosen
+    if T > 3:
+        idx[2:] = torch.where(idx[2:] == 3, torch.full_like(idx[2:], 5), idx[2:])                        # ... except here; 3 hardly
+        idx[1] = torch.tensor([4, 0])
+    wts = torch.rand(T, top, generator=g)
+    wts = wts / wts.sum(-1, keepdim=True)
+    f = h.double()
+    want = torch.zeros(T, H, dtype=F64)
+    for t in range(T):
+        for e, a in zip(idx[t].tolist(), wts[t].tolist()):
+            act = (pp.silu(gu[e, 0].double() @ f[t]) * (gu[e, 1].double() @ f[t])).to(dt).double()       # the engine rounds between the products
+            want[t] += a * (dn[e].double() @ act)
+    want = (0.6 * want).float()
+    few = ops.experts_few(h.cuda(), gu.cuda(), dn.cuda(), idx.cuda(), wts.cuda(), 0.6).cpu()
+    torch.testing.assert_close(few, want, **tol_of(dtype, 2e-5, 2e-2))
+    counts, place = ops.expert_order(idx.cuda(), E)
+    assert counts.cpu().tolist() == [int((idx == e).sum()) for e in range(E)]
+    flat = idx.reshape(-1)
+    order = sorted(range(T * top), key=lambda i: (int(flat[i]), i))
+    assert place.cpu().tolist() == [order.index(i) for i in range(T * top)]
+    rows = ops.expert_gather(h.cuda(), place, top).cpu()
+    for i, at in enumerate(place.cpu().tolist()):
+        assert torch.equal(rows[at], h[i // top])
+    y = torch.randn(T * top, H, generator=g)
+    got = ops.expert_combine(y.cuda(), place, wts.cuda(), 0.6).cpu()
+    pl = place.cpu().tolist()
+    w2 = torch.stack([sum(wts[t, k] * y[pl[t * top + k]] for k in range(top)) for t in range(T)]) * 0.6
+    torch.testing.assert_close(got, w2, rtol=1e-5, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# the model through the step function
+# ---------------------------------------------------------------------------------------------------------------------
+LENGTHS = {"PA": 61, "PB": 40, "PC": 75}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["PA", "PB", "PC"])
+def test_whole_prompt_token_by_token_and_in_portions(name, dtype):
+    """The same sequence three ways: one step; five tokens and then one token a step (through the CUDA graph); portions of
+    changing sizes down to two tokens.  Every position against the plain implementation."""
+    V = CONFIGS_P[name]["vocab"]
+    n = LENGTHS[name]
+    toks = random_tokens(n, V, 100 + n)
+    seqs = {"w": toks, "d": toks, "p": toks}
+    r = runner(name, dtype, num_pages=3 * (-(-n // PAGE[name])) + 8)
+    poison(r)
+    got = play(r, [{"entries": [("w", toks, list(range(n)))], "end": ["w"]}])
+    compare(name, dtype, got, seqs)
+    steps = [{"entries": [("d", toks[:5], list(range(5)))]}] + [{"entries": [("d", [t], [0])]} for t in toks[5:]]
+    got = play(r, steps)
+    assert r.last_step_used_graph
+    compare(name, dtype, got, seqs)
+    sizes, at, steps = [2, 3, 7, 2, 16, 1, 1, 2, 5, 2, 9], 0, []
+    while at < n:
+        c = min(sizes[len(steps) % len(sizes)], n - at)
+        steps.append({"entries": [("p", toks[at:at + c], list(range(c)))]})
+        at += c
+    got = play(r, steps)
+    compare(name, dtype, got, seqs)
+    assert len(got) == n
+    r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["PA", "PB", "PC"])
+def test_mixed_batches_on_a_small_pool(name, dtype):
+    """Five requests of unequal lengths through two request slots and a pool that holds little more than the two longest:
+    portions of one beside single tokens of another; pages, block-table rows and state rows are used again, and what
+    they held before (NaN at the start) must never be read."""
+    V = CONFIGS_P[name]["vocab"]
+    P = PAGE[name]
+    lens = {"a": 50, "b": 23, "c": 1, "d": 66, "e": 34}
+    seqs = {k: random_tokens(n, V, 7 + n) for k, n in lens.items()}
+    r = runner(name, dtype, num_pages=-(-66 // P) + -(-50 // P) + 1, max_reqs=2)
+    poison(r)
+    a, b, c, d, e = (seqs[k] for k in "abcde")
+    steps = [
+        {"entries": [("a", a[:17], [0, 16]), ("b", b[:2], [1])]},
+        {"entries": [("b", b[2:3], [0]), ("a", a[17:40], [5, 22])]},
+        {"entries": [("a", a[40:41], [0]), ("b", b[3:23], list(range(20)))], "end": ["b"]},
+        {"entries": [("c", c, [0]), ("a", a[41:42], [0])], "end": ["c"]},
+        {"entries": [("a", a[42:43], [0]), ("d", d[:30], [29])]},
+        {"entries": [("d", d[30:60], [0, 29]), ("a", a[43:50], list(range(7)))], "end": ["a"]},
+        {"entries": [("d", d[60:61], [0]), ("e", e[:9], [8])]},
+        {"entries": [("e", e[9:11], [0, 1]), ("d", d[61:62], [0])]},
+    ] + [{"entries": [("d", d[62 + i:63 + i], [0]), ("e", e[11 + i:12 + i], [0])]} for i in range(4)] + [
+        {"entries": [("e", e[15:34], [18])], "end": ["d", "e"]},
+    ]
+    got = play(r, steps)
+    compare(name, dtype, got, seqs)
+    r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["PA", "PC"])
+def test_long_decoding(name, dtype):
+    """Two requests decode together for 330 steps through the CUDA graph, past the point where a decoded token's keys are cut
+    into pieces and past several changes of the query's factor; a third joins late with a portion and leaves early."""
+    V = CONFIGS_P[name]["vocab"]
+    a, b, c = random_tokens(345, V, 1), random_tokens(352, V, 2), random_tokens(30, V, 3)
+    seqs = {"a": a, "b": b, "c": c}
+    r = runner(name, dtype, num_pages=-(-800 // PAGE[name]) + 4, max_reqs=3)
+    poison(r)
+    steps = [{"entries": [("a", a[:10], [9]), ("b", b[:20], [19])]}]
+    for i in range(330):
+        es = [("a", [a[10 + i]], [0]), ("b", [b[20 + i]], [0])]
+        if i == 200:
+            es.append(("c", c[:26], [25]))
+        elif 200 < i <= 204:
+            es.append(("c", [c[25 + i - 200]], [0]))
+        steps.append({"entries": es, "end": ["c"] if i == 204 else []})
+    got = play(r, steps)
+    assert r.last_step_used_graph
+    compare(name, dtype, got, seqs)
+    r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_page_sizes(dtype):
+    """Pages of one token and pages wider than a request, the same three ways."""
+    for name, P in (("PA", 1), ("PB", 64), ("PC", 2)):
+        V = CONFIGS_P[name]["vocab"]
+        toks, other = random_tokens(45, V, 31), random_tokens(20, V, 32)
+        seqs = {"w": toks, "p": toks, "o": other}
+        r = runner(name, dtype, num_pages=3 * (-(-45 // P)) + 4, page_size=P)
+        poison(r)
+        got = play(r, [{"entries": [("w", toks, list(range(45)))], "end": ["w"]}])
+        steps = [{"entries": [("p", toks[:2], [0, 1]), ("o", other[:11], [10])]}]
+        steps += [{"entries": [("p", toks[2 + 5 * i:7 + 5 * i], list(range(5))), ("o", [other[11 + i]], [0])]} for i in range(8)]
+        steps += [{"entries": [("p", toks[42:45], [0, 1, 2]), ("o", [other[19]], [0])]}]
+        got.update(play(r, steps))
+        compare(name, dtype, got, seqs)
+        r.mgr.check_idle()
+
+
+def _random_config(seed):
+    """A seeded Pepevik configuration: two to five layers of either kind in any order with either feed-forward or none, some
+    of them further runs of an earlier layer's weights."""
+    import random
+    from tiny_pepevik import dense, layer, model, moe, par, ssm
+    rnd = random.Random(seed)
+    width = rnd.choice([40, 64, 72, 128])
+    layers = []
+    for i in range(rnd.randint(2, 5)):
+        if layers and rnd.random() < 0.25:
+            j = rnd.randrange(len(layers))
+            src = dict(layers[j])
+            src.pop("weights_of", None)
+            layers.append(dict(src, weights_of=j))
+            continue
+        if rnd.random() < 0.5:
+            kv = rnd.choice([1, 2, 3])
+            mixer = par(kv * rnd.choice([1, 2, 4]), kv, rnd.choice([8, 20, 48, 96]), rnd.choice([8, 24, 40, 64]), rnd.choice([16, 50, 128]),
+                        scale=rnd.choice([None, 0.2]), temp=rnd.choice([None, (0.5, 4), (1.0, 16), (0.25, 1)]))
+        else:
+            groups = rnd.choice([1, 2])
+            mixer = ssm(groups * rnd.choice([1, 2, 3]), rnd.choice([8, 12, 32]), rnd.choice([4, 16, 24, 64]), groups=groups,
+                        conv=rnd.choice([1, 2, 3, 4]), norm_groups=rnd.choice([1, groups]))
+        kind = rnd.random()
+        if kind < 0.2:
+            mlp = None
+        elif kind < 0.5:
+            mlp = dense(rnd.choice([32, 100]))
+        else:
+            count = rnd.choice([1, 2, 4])
+            per = rnd.choice([1, 2, 3])
+            keep = rnd.randint(1, count)
+            mlp = moe(count * per, rnd.randint(1, min(keep * per, 4)), rnd.choice([8, 24]), count=count, keep=keep)
+        layers.append(layer(mixer, mlp))
+    return model(width, rnd.choice([50, 97, 200]), rnd.choice([1e-5, 1e-6]), layers, max_positions=rnd.choice([128, 300]),
+                 residual_mult=rnd.choice([None, 0.5, 0.8]), embedding_scale=rnd.choice([None, 2.0, 6.0]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(seed):
+    """Whole, token by token and in portions beside another request's single tokens, float32 (the logic) and bfloat16."""
+    from mini_sglang_b200.engine.step import ModelRunner
+    cfg = _random_config(seed)
+    w = make_weights(cfg, 100 + seed)
+    path = write_model_dir(os.path.join(_tmp.name, f"random{seed}"), cfg, w)
+    V = cfg["vocab"]
+    toks, other = random_tokens(70, V, seed), random_tokens(40, V, 50 + seed)
+    with torch.no_grad():
+        ref = {"w": pp.forward_sequence(cfg, w, toks).float(), "o": pp.forward_sequence(cfg, w, other).float()}
+    ref["d"] = ref["p"] = ref["w"]
+    P = [1, 4, 16, 8][seed % 4]
+    for dtype in ("float32", "bfloat16"):
+        r = ModelRunner.from_model_dir(path, dtype=dtype, page_size=P, num_pages=3 * (-(-70 // P)) + 6, max_reqs=2, max_context_len=128)
+        poison(r)
+        got = play(r, [{"entries": [("w", toks, list(range(70)))], "end": ["w"]}])
+        steps = [{"entries": [("d", toks[:3], [0, 1, 2])]}] + [{"entries": [("d", [t], [0])]} for t in toks[3:]]
+        got.update(play(r, steps))
+        steps = [{"entries": [("o", other[:9], [8]), ("p", toks[:2], [0, 1])]}]
+        steps += [{"entries": [("p", toks[2 + 4 * i:6 + 4 * i], [0, 1, 2, 3]), ("o", [other[9 + i]], [0])]} for i in range(17)]
+        got.update(play(r, steps))
+        compare(f"random {seed}", dtype, got, None, ref=ref, bound=0.05)
+        r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(dtype):
+    """Engine.generate with the scheduler: prompts of unequal lengths, portions of at most 16 tokens, a small pool."""
+    from mini_sglang_b200 import Engine, EngineArgs
+    name = "PA"
+    cfg = CONFIGS_P[name]
+    prompts = [random_tokens(n, cfg["vocab"], 50 + n) for n in (5, 33, 18)]
+    eng = Engine(EngineArgs(model=model_dir(name), dtype=dtype, page_size=4, num_pages=48, max_num_reqs=3, random_seed=0,
+                            chunk_size=16, max_context_len=256, log_level="WARNING"))
+    outs = eng.generate(input_ids=prompts, sampling_params={"temperature": 0.0, "max_new_tokens": 12, "ignore_eos": True})
+    for p, o in zip(prompts, outs):
+        got = o["token_ids"]
+        assert len(got) == 12
+        if dtype == "float32":
+            assert got == pp.greedy_generate(cfg, weights(name), p, 12)
+        else:
+            toks = list(p)
+            for t in got:           # bfloat16 may take another of two nearly equal logits
+                with torch.no_grad():
+                    row = pp.forward_sequence(cfg, weights(name), toks)[-1]
+                assert float(row.max() - row[t]) < 0.05 * float(row.std()) + 0.05
+                toks.append(t)
+    eng.scheduler.check_idle_invariants()
+
+
+def test_trace_replay_program(tmp_path):
+    name = "PB"
+    V = CONFIGS_P[name]["vocab"]
+    a, b = random_tokens(37, V, 1), random_tokens(21, V, 2)
+    lines = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [0, 19]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[20:35], "want": []}, {"id": "b", "tokens": b[:21], "want": [20]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[35:36], "want": [0]}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[36:37], "want": [0]}], "end": ["a"]},
+    ]
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir(name), "--dtype", dtype,
+                               "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(l) for l in lines) + "\n",
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(4)]
+        ra, rb = plain(name, tuple(a)), plain(name, tuple(b))
+        rd = lambda i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))        # noqa: E731
+        for got, want in ((rd(0), ra[[0, 19]]), (rd(1), rb[[20]]), (rd(2), ra[[35]]), (rd(3), ra[[36]])):
+            assert got.shape == want.shape
+            for g_row, w_row in zip(got, want):
+                row_close(g_row, w_row, dtype)
