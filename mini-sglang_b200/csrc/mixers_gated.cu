@@ -289,6 +289,260 @@ __global__ void __launch_bounds__(SA_ROWS * 32) sigmoid_attention_kernel(const S
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16, prompts and portions): S = Q K^T and O += P V by mma.sync m16n8k16 with
+// float32 accumulators, P = sigmoid(S * scale + bias[head][distance]) in float32 between them, rounded to bfloat16 only as
+// the operand of the value product.  A block owns 64 rows = 64 / G tokens x the G query heads of one kv head (so a key tile
+// serves all its heads) and walks the keys in tiles of 64 anchored at multiples of 64, two tiles in flight (cp.async).
+// DK, DV: the head sizes rounded up to a size the kernel is built for; columns beyond d, dv are zero in shared memory.
+// ---------------------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_u32(unsigned s, const void* gmem, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4_u32(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_u32(unsigned (&r)[4], unsigned s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+// 1 / (1 + e^-x) with the special-function unit's 2^x and reciprocal (relative error about 2^-21; -inf gives 0)
+__device__ __forceinline__ float fast_sigmoid(float x) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(-1.4426950408889634f * x));
+    return __fdividef(1.f, 1.f + e);
+}
+}  // namespace
+
+#define SAM_R 64            // rows of a block
+#define SAM_KT 64           // keys of a tile
+#define SAM_THREADS 128
+#define SAM_BS_HEADS 8      // heads of a block whose bias entries go through shared memory
+#define SAM_BS_LD 136
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(SAM_THREADS) sigmoid_attention_mma_kernel(const SigmoidAttnParams p) {
+    constexpr int LDK = DK + 8, LDV = DV + 8;           // padded rows (elements): ldmatrix without bank conflicts
+    constexpr int NKB = SAM_KT / 8, NDB = DV / 8;
+    constexpr int CHK = DK / 8, CHV = DV / 8;           // 16-byte pieces of a row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [64][LDK]
+    __nv_bfloat16* KVs = Qs + SAM_R * LDK;                                          // [stage][K: 64 x LDK | V: 64 x LDV]
+    __shared__ float bias_s[SAM_BS_HEADS * SAM_BS_LD];
+    __shared__ int tile_sh[2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.n_q / p.n_kv;
+    const int Gc = G <= SAM_R ? G : SAM_R;
+    const int n_chunks = G <= SAM_R ? 1 : (G + SAM_R - 1) / SAM_R;
+    const int QT = G <= SAM_R ? SAM_R / G : 1;
+    const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
+    if (tid == 0) {
+        if (p.uniform) {
+            tile_sh[0] = blockIdx.x; tile_sh[1] = 0;
+        } else {
+            // heaviest tiles first: the last tiles of a request walk the most keys, and blocks start in index order
+            int left = (int)gridDim.x - 1 - (int)blockIdx.x, found = -1, at = 0;
+            for (int r = 0; r < p.B; ++r) {
+                const int nt = (p.q_start[r + 1] - p.q_start[r] + QT - 1) / QT;
+                if (left < nt) { found = r; at = left * QT; break; }
+                left -= nt;
+            }
+            tile_sh[0] = found; tile_sh[1] = at;
+        }
+    }
+    __syncthreads();
+    const int req = tile_sh[0], t0 = tile_sh[1];
+    if (req < 0 || req >= p.B) return;
+    const int q_base = p.q_start[req], q_len = p.q_start[req + 1] - q_base, kv_len = p.kv_len[req];
+    const int n_tok = min(QT, q_len - t0);
+    if (n_tok <= 0) return;
+    const int p_min = kv_len - q_len + t0, p_max = p_min + n_tok - 1;
+    // key tiles this block walks: all up to the last position's, or (one-token steps) those of its piece; a piece is a whole
+    // number of tiles, so a tile never holds keys of two pieces
+    int kt_lo = 0, kt_hi = p_max / SAM_KT + 1;
+    if (p.splits > 1) {
+        kt_lo = (int)blockIdx.z * (p.split_keys / SAM_KT);
+        kt_hi = min(kt_hi, kt_lo + p.split_keys / SAM_KT);
+        if (kt_lo >= kt_hi) return;
+    }
+    const int d = p.d, dv = p.dv;
+    const __nv_bfloat16* qg = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(p.k_cache);
+    const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(p.v_cache);
+    const int* bt = p.block_table + (size_t)req * p.bt_stride;
+    const unsigned q_s = smem_u32(Qs), kv_s = smem_u32(KVs);
+    constexpr unsigned K_BYTES = SAM_KT * LDK * 2u, STAGE_BYTES = K_BYTES + SAM_KT * LDV * 2u;
+
+    // ---- the block's query rows (zero where the tile has no token or head, and beyond d)
+    for (int idx = tid; idx < SAM_R * CHK; idx += SAM_THREADS) {
+        const int r = idx / CHK, c = idx - r * CHK;
+        const int tl = r / Gc, hl = r - tl * Gc, hg = chunk * SAM_R + hl;
+        const bool valid = tl < n_tok && tl < QT && hg < G && c * 8 < d;
+        const size_t tok = (size_t)(q_base + t0 + (valid ? tl : 0));
+        const __nv_bfloat16* src = qg + (tok * p.n_q + (size_t)kvh * G + (valid ? hg : 0)) * d + (valid ? c * 8 : 0);
+        cp_async16_u32(q_s + (unsigned)(r * LDK + c * 8) * 2u, src, valid);
+    }
+    // a thread copies half a row of K and of V per tile: row tid / 2, every second 16-byte piece
+    const int ld_row = tid >> 1, ld_half = tid & 1;
+    auto load_kv = [&](int stage, int kt) {
+        const int key = kt * SAM_KT + ld_row;
+        const bool live = key <= p_max;
+        size_t row = 0;
+        if (live) row = ((size_t)bt[key / p.page_size] * p.n_kv + kvh) * p.page_size + (key % p.page_size);
+        const unsigned ks = kv_s + (unsigned)stage * STAGE_BYTES + (unsigned)(ld_row * LDK) * 2u;
+        const unsigned vs = kv_s + (unsigned)stage * STAGE_BYTES + K_BYTES + (unsigned)(ld_row * LDV) * 2u;
+#pragma unroll
+        for (int c = ld_half; c < CHK; c += 2) {
+            const bool ok = live && c * 8 < d;
+            cp_async16_u32(ks + c * 16, kc + row * d + (ok ? c * 8 : 0), ok);
+        }
+#pragma unroll
+        for (int c = ld_half; c < CHV; c += 2) {
+            const bool ok = live && c * 8 < dv;
+            cp_async16_u32(vs + c * 16, vc + row * dv + (ok ? c * 8 : 0), ok);
+        }
+    };
+    load_kv(0, kt_lo);
+    cp_async_commit();
+
+    const int row_base = warp * 16;
+    const bool warp_live = row_base / Gc < n_tok;       // else all 16 rows of the warp are empty: it copies, but multiplies nothing
+    const int r_lo = row_base + (lane >> 2), r_hi = r_lo + 8;
+    const int tl_lo = r_lo / Gc, tl_hi = r_hi / Gc;
+    const int hl_lo = r_lo - tl_lo * Gc, hl_hi = r_hi - tl_hi * Gc;
+    const int pos_lo = p_min + tl_lo, pos_hi = p_min + tl_hi;
+    const float* bias_lo = p.bias + (size_t)min(kvh * G + chunk * SAM_R + hl_lo, p.n_q - 1) * p.bias_len;
+    const float* bias_hi = p.bias + (size_t)min(kvh * G + chunk * SAM_R + hl_hi, p.n_q - 1) * p.bias_len;
+    // The bias of a key tile through shared memory: entry j of a head stands for the distance dmin + j with dmin = p_min - (last
+    // key of the tile), and the row of token tl reads key kk of the tile at tl + 63 - kk.
+    const bool bias_staged = Gc <= SAM_BS_HEADS;
+    const float* bs_lo = bias_s + hl_lo * SAM_BS_LD + tl_lo + (SAM_KT - 1) - (lane & 3) * 2;
+    const float* bs_hi = bias_s + hl_hi * SAM_BS_LD + tl_hi + (SAM_KT - 1) - (lane & 3) * 2;
+    const unsigned q_a = q_s + (unsigned)((row_base + (lane & 15)) * LDK + (lane >> 4) * 8) * 2u;
+    const unsigned k_lane = (unsigned)(((lane & 7) + ((lane >> 4) & 1) * 8) * LDK + ((lane >> 3) & 1) * 8) * 2u;
+    const unsigned v_lane = (unsigned)(((lane & 7) + ((lane >> 3) & 1) * 8) * LDV + ((lane >> 4) & 1) * 8) * 2u;
+
+    float o[NDB][4];
+#pragma unroll
+    for (int i = 0; i < NDB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    for (int kt = kt_lo; kt < kt_hi; ++kt) {
+        const int stage = (kt - kt_lo) & 1;
+        if (bias_staged) {       // written before the barrier below, read after it, and not written again before the one that ends the tile
+            const int dmin = p_min - (kt * SAM_KT + SAM_KT - 1), span = QT + SAM_KT - 1;
+            for (int idx = tid; idx < Gc * span; idx += SAM_THREADS) {
+                const int hl = idx / span, j = idx - hl * span;
+                const int head = min(kvh * G + chunk * SAM_R + hl, p.n_q - 1);
+                bias_s[hl * SAM_BS_LD + j] = p.bias[(size_t)head * p.bias_len + min(max(dmin + j, 0), p.bias_len - 1)];
+            }
+        }
+        if (kt + 1 < kt_hi) {
+            load_kv(stage ^ 1, kt + 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key0 = kt * SAM_KT;
+        if (!warp_live || key0 > p_min + (row_base + 15) / Gc) {      // no row of the warp sees a key of this tile
+            __syncthreads();
+            continue;
+        }
+        const unsigned ks_a = kv_s + (unsigned)stage * STAGE_BYTES + k_lane;
+        const unsigned vs_a = kv_s + (unsigned)stage * STAGE_BYTES + K_BYTES + v_lane;
+
+        float s[NKB][4];
+#pragma unroll
+        for (int i = 0; i < NKB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk) {
+            unsigned a[4];
+            ldmatrix_x4_u32(a, q_a + kk * 32);
+#pragma unroll
+            for (int nb2 = 0; nb2 < NKB / 2; ++nb2) {
+                unsigned b[4];
+                ldmatrix_x4_u32(b, ks_a + (unsigned)(nb2 * 16 * LDK + kk * 16) * 2u);
+                mma_bf16_16816(s[2 * nb2], a, b[0], b[1]);
+                mma_bf16_16816(s[2 * nb2 + 1], a, b[2], b[3]);
+            }
+        }
+        // ---- weights: every key by itself
+        const bool need_mask = key0 + SAM_KT - 1 > p_min;
+#pragma unroll
+        for (int nb = 0; nb < NKB; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                const int pos = (e < 2) ? pos_lo : pos_hi;
+                float w = 0.f;
+                if (!need_mask || key <= pos) {
+                    const float b = bias_staged ? ((e < 2) ? bs_lo : bs_hi)[-(nb * 8 + (e & 1))]
+                                                : ((e < 2) ? bias_lo : bias_hi)[min(max(pos - key, 0), p.bias_len - 1)];
+                    w = fast_sigmoid(fmaf(s[nb][e], p.scale, b));
+                }
+                s[nb][e] = w;
+            }
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int j = 0; j < NKB / 2; ++j) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+            a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+            a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+            a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+            for (int nd2 = 0; nd2 < DV / 16; ++nd2) {
+                unsigned b[4];
+                ldmatrix_x4_trans_u32(b, vs_a + (unsigned)(j * 16 * LDV + nd2 * 16) * 2u);
+                mma_bf16_16816(o[2 * nd2], a, b[0], b[1]);
+                mma_bf16_16816(o[2 * nd2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int tl = half ? tl_hi : tl_lo, hl = half ? hl_hi : hl_lo, hg = chunk * SAM_R + hl;
+        if (!(tl < n_tok && tl < QT && hg < G)) continue;
+        if (p.splits > 1) {
+            float* pg = p.part + (((size_t)blockIdx.z * p.T + (q_base + t0 + tl)) * p.n_q + (kvh * G + hg)) * dv;
+#pragma unroll
+            for (int nd = 0; nd < NDB; ++nd) {
+                const int col = nd * 8 + (lane & 3) * 2;
+                if (col < dv) *reinterpret_cast<float2*>(pg + col) = make_float2(o[nd][half * 2], o[nd][half * 2 + 1]);
+            }
+            continue;
+        }
+        __nv_bfloat16* dst = og + (size_t)(q_base + t0 + tl) * p.out_stride + (size_t)(kvh * G + hg) * dv;
+#pragma unroll
+        for (int nd = 0; nd < NDB; ++nd) {
+            const int col = nd * 8 + (lane & 3) * 2;
+            if (col < dv)           // dv is a multiple of 8: a pair lies inside the row or outside it
+                *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[nd][half * 2], o[nd][half * 2 + 1]);
+        }
+    }
+}
+
 // out[t, c] = sum over the pieces s, in order, of part[s][t][c]; only the pieces that hold keys of the token's request
 template <typename T>
 __global__ void sum_pieces_kernel(const float* __restrict__ part, const int* __restrict__ kv_len, const int* __restrict__ token_req,
@@ -349,6 +603,55 @@ MSGL_API int msgl_sigmoid_attention(const void* q, const void* k_cache, const vo
     return msgl_check_launch();
 }
 
+// The tensor-core launch: bfloat16, head sizes that are multiples of 8 up to 128, rows of `out` that pairs of elements can be
+// stored into.  n_tiles: the sum over the requests of ceil(tokens / QT) with QT = 64 / (heads per kv head) (1 beyond 64), or
+// with `uniform` (every request brings one token) the number of requests; then `splits` pieces of `split_keys` keys (a
+// multiple of 64) go to blocks of their own, which leave float32 sums in `part` for sum_pieces_kernel.
+MSGL_API int msgl_sigmoid_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
+                                        const int* block_table, int bt_stride, int uniform, int n_tiles, const float* bias, int bias_len,
+                                        void* out, long long out_stride, float* part, int splits, int split_keys, int T_, int B, int n_q,
+                                        int n_kv, int d, int dv, int page_size, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0) return MSGL_OK;
+    if (d <= 0 || dv <= 0 || d > 128 || dv > 128 || d % 8 || dv % 8 || n_kv <= 0 || n_q % n_kv || page_size < 1 || bias == nullptr ||
+        bias_len < 1 || (out_stride & 1) || ((size_t)out & 3) || splits < 1 ||
+        (splits > 1 && (!uniform || part == nullptr || split_keys < SAM_KT || split_keys % SAM_KT || ((size_t)part & 7))))
+        return MSGL_ERR_SIZE;
+    SigmoidAttnParams p;
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
+    p.bt_stride = bt_stride; p.uniform = uniform; p.bias = bias; p.bias_len = bias_len; p.out = out; p.out_stride = out_stride;
+    p.part = part; p.splits = splits; p.split_keys = split_keys; p.T = T_; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.d = d; p.dv = dv;
+    p.page_size = page_size; p.QT = 0; p.GH = 0; p.scale = scale;
+    const int G = n_q / n_kv;
+    const dim3 grid(n_tiles, n_kv * (G <= SAM_R ? 1 : (G + SAM_R - 1) / SAM_R), splits);
+#define SAM_LAUNCH(DK, DV)                                                                                                   \
+    do {                                                                                                                     \
+        const size_t smem = ((size_t)SAM_R * (DK + 8) + 2 * ((size_t)SAM_KT * (DK + 8) + (size_t)SAM_KT * (DV + 8))) * 2;    \
+        static MsglOncePerDevice once;                                                                                       \
+        if (once.due()) {                                                                                                    \
+            cudaFuncSetAttribute(sigmoid_attention_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            once.mark();                                                                                                     \
+        }                                                                                                                    \
+        sigmoid_attention_mma_kernel<DK, DV><<<grid, SAM_THREADS, smem, stream>>>(p);                                        \
+    } while (0)
+#define SAM_BY_DV(DK)                                                                                                        \
+    do {                                                                                                                     \
+        if (dv <= 64) SAM_LAUNCH(DK, 64);                                                                                    \
+        else if (dv <= 96) SAM_LAUNCH(DK, 96);                                                                               \
+        else SAM_LAUNCH(DK, 128);                                                                                            \
+    } while (0)
+    if (d <= 64) SAM_BY_DV(64);
+    else if (d <= 96) SAM_BY_DV(96);
+    else SAM_BY_DV(128);
+#undef SAM_BY_DV
+#undef SAM_LAUNCH
+    int code = msgl_check_launch();
+    if (code != MSGL_OK || splits <= 1) return code;
+    const int N = n_q * dv;
+    const dim3 g2(T_, max(1, min((N + 255) / 256, 16)));
+    sum_pieces_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>(part, kv_len, nullptr, (__nv_bfloat16*)out, out_stride, T_, N, splits, split_keys);
+    return msgl_check_launch();
+}
+
 // ---------------------------------------------------------------------------------------
 // minGRU: a gated recurrence per channel whose gates read the current token only
 //
@@ -399,6 +702,104 @@ MSGL_API int msgl_mingru(const void* proj, long long stride, int z_off, int x_of
     if (dtype == MSGL_F32) mingru_kernel<float><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, out, out_stride, c_out);
     else if (dtype == MSGL_BF16) mingru_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, out, out_stride, c_out);
     else return MSGL_ERR_DTYPE;
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// minGRU over long portions: the tokens of a request in chunks of `L` that run side by side.  The recurrence S_t = a_t S_(t-1) + b_t
+// (a = 1 - z, b = z * candidate) of a chunk is S_end = A S_start + E with A = the product of its a and E = its end state from
+// zero.  mingru_chunk_sum_kernel leaves (A, E) of every chunk in `sums` [chunk][2][W] and the request's state before the step in
+// `init` [request][W]; mingru_chunk_out_kernel brings a chunk's S_start up from `init` through the chunks before it, walks
+// the chunk and writes the outputs; the last chunk of a request writes the state back.  Float32 throughout; the result differs
+// from the token-by-token kernel by rounding only.  Block y = chunk (over all requests, in order), thread = channel.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ bool mingru_find_chunk(const int* __restrict__ q_start, int B, int L, int* sh, int& req, int& first, int& c0) {
+    if (threadIdx.x == 0) {
+        int left = blockIdx.y, found = -1, base = 0;
+        for (int r = 0; r < B; ++r) {
+            const int nc = (q_start[r + 1] - q_start[r] + L - 1) / L;
+            if (left < nc) { found = r; break; }
+            left -= nc; base += nc;
+        }
+        sh[0] = found; sh[1] = base; sh[2] = left;
+    }
+    __syncthreads();
+    req = sh[0]; first = sh[1]; c0 = sh[2];
+    return req >= 0;
+}
+
+template <typename T>
+__global__ void mingru_chunk_sum_kernel(const void* proj_, long long stride, int z_off, int x_off, int W, const float* __restrict__ bz,
+                                        const float* __restrict__ bx, const float* __restrict__ state, const int* __restrict__ q_start,
+                                        const int* __restrict__ slots, int B, int L, float* __restrict__ sums, float* __restrict__ init) {
+    __shared__ int sh[3];
+    int r, first, ci;
+    if (!mingru_find_chunk(q_start, B, L, sh, r, first, ci)) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    if (ci == 0) init[(size_t)r * W + c] = state[(size_t)slots[r] * W + c];
+    const int t0 = q_start[r] + ci * L, n = min(L, q_start[r + 1] - t0);
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    const float b_z = bz[c], b_x = bx[c];
+    float A = 1.f, E = 0.f;
+    for (int tt = 0; tt < n; ++tt) {
+        const T* row = proj + (size_t)(t0 + tt) * stride;
+        const float z = sigmoidf_(to_f32<T>(row[z_off + c]) + b_z), a = to_f32<T>(row[x_off + c]) + b_x;
+        const float cand = a >= 0.f ? a + 0.5f : sigmoidf_(a);
+        A *= 1.f - z;
+        E = (1.f - z) * E + z * cand;
+    }
+    float* o = sums + (size_t)(first + ci) * 2 * W;
+    o[c] = A; o[W + c] = E;
+}
+
+template <typename T>
+__global__ void mingru_chunk_out_kernel(const void* proj_, long long stride, int z_off, int x_off, int g_off, int W,
+                                        const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state,
+                                        const int* __restrict__ q_start, const int* __restrict__ slots, int B, int L,
+                                        const float* __restrict__ sums, const float* __restrict__ init, void* out_, long long out_stride,
+                                        float c_out) {
+    __shared__ int sh[3];
+    int r, first, ci;
+    if (!mingru_find_chunk(q_start, B, L, sh, r, first, ci)) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    float S = init[(size_t)r * W + c];
+    for (int k = 0; k < ci; ++k) {
+        const float* o = sums + (size_t)(first + k) * 2 * W;
+        S = fmaf(o[c], S, o[W + c]);
+    }
+    const int t0 = q_start[r] + ci * L, n = min(L, q_start[r + 1] - t0);
+    const T* proj = reinterpret_cast<const T*>(proj_);
+    T* out = reinterpret_cast<T*>(out_);
+    const float b_z = bz[c], b_x = bx[c];
+    for (int tt = 0; tt < n; ++tt) {
+        const T* row = proj + (size_t)(t0 + tt) * stride;
+        const float z = sigmoidf_(to_f32<T>(row[z_off + c]) + b_z), a = to_f32<T>(row[x_off + c]) + b_x;
+        const float pg = to_f32<T>(row[g_off + c]);
+        const float cand = a >= 0.f ? a + 0.5f : sigmoidf_(a);
+        S = (1.f - z) * S + z * cand;
+        out[(size_t)(t0 + tt) * out_stride + c] = from_f32<T>(S * siluf_(pg) * c_out);
+    }
+    if (t0 + n == q_start[r + 1]) state[(size_t)slots[r] * W + c] = S;
+}
+
+// n_chunks: the sum over the requests of ceil(tokens / L); sums: float32 [n_chunks][2][W]; init: float32 [B][W]
+MSGL_API int msgl_mingru_chunked(const void* proj, long long stride, int z_off, int x_off, int g_off, int W, const float* bz, const float* bx,
+                                 float* state, const int* q_start, const int* slots, void* out, long long out_stride, float c_out, int B,
+                                 int L, int n_chunks, float* sums, float* init, int dtype, cudaStream_t stream) {
+    if (B <= 0 || n_chunks <= 0) return MSGL_OK;
+    if (W <= 0 || L < 1 || sums == nullptr || init == nullptr || n_chunks > 65535) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int threads = 128;
+    const dim3 grid((W + threads - 1) / threads, n_chunks);
+    if (dtype == MSGL_F32) {
+        mingru_chunk_sum_kernel<float><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, W, bz, bx, state, q_start, slots, B, L, sums, init);
+        mingru_chunk_out_kernel<float><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, B, L, sums, init, out, out_stride, c_out);
+    } else {
+        mingru_chunk_sum_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, W, bz, bx, state, q_start, slots, B, L, sums, init);
+        mingru_chunk_out_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(proj, stride, z_off, x_off, g_off, W, bz, bx, state, q_start, slots, B, L, sums, init, out, out_stride, c_out);
+    }
     return msgl_check_launch();
 }
 
@@ -511,13 +912,20 @@ MSGL_API int msgl_causal_conv_act(const void* in, long long stride, int off, int
 #define SS_COLS 32
 #define SS_PARTS 8
 #define SS_MAX_ROWS 64      // state sizes up to SS_PARTS * SS_MAX_ROWS
+#define SS_TB 8             // tokens whose B, C, x, decay and step lie in shared memory together
 
+// The tokens go through shared memory in batches of SS_TB, two batches in flight: a thread loads its share of the next batch into
+// registers before it walks the current one and puts them down afterwards, so a token costs its multiply-adds, not a wait for
+// memory.  A batch row is [B: N | C: N | x: SS_COLS | decay | step]; the thread that brings a token's dt makes decay and step.
+// The sums of a token are the same, in the same order, however the tokens were cut into steps.
 template <typename T, int NR>
 __global__ void __launch_bounds__(SS_COLS * SS_PARTS)
 ssm_scan_kernel(const void* xbc_, int heads, int groups, int N, int P, const void* proj_, long long stride, int dt_off,
                 const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
                 float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y) {
-    extern __shared__ float bc[];                    // [2][2][N]: double-buffered B and C of the current token
+    extern __shared__ float sm[];                    // [2][SS_TB][2 N + SS_COLS + 2]
+    constexpr int NT = SS_COLS * SS_PARTS;
+    constexpr int PF = (SS_TB * (2 * SS_PARTS * NR + SS_COLS + 1) + NT - 1) / NT;
     const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SS_COLS;
     const int tid = threadIdx.x;
     const int part = tid & (SS_PARTS - 1), col = col0 + (tid >> 3);
@@ -537,33 +945,78 @@ ssm_scan_kernel(const void* xbc_, int heads, int groups, int N, int P, const voi
         s[j] = (j < rows && i < N && col_ok) ? S[(size_t)i * P + col] : 0.f;
     }
     const float a = -expf(A_log[h]), bias = dt_bias[h], dskip = Dskip[h];
-    for (int tt = 0; tt < n; ++tt) {
-        const size_t row = (size_t)(t0 + tt) * C_;
-        float* Bb = bc + (tt & 1) * 2 * N;
-        float* Cb = Bb + N;
-        for (int i = tid; i < N; i += SS_COLS * SS_PARTS) {
-            Bb[i] = to_f32<T>(xbc[row + inner + g * N + i]);
-            Cb[i] = to_f32<T>(xbc[row + inner + groups * N + g * N + i]);
+    const int ROW = 2 * N + SS_COLS + 1, ROWS = ROW + 1, EB = SS_TB * ROW;
+    auto fetch = [&](int e, int tb0, int nb) -> float {          // element e of the batch of nb tokens that starts at token tb0
+        const int tt = e / ROW, k = e - tt * ROW;
+        if (tt >= nb) return 0.f;
+        const size_t t = (size_t)(t0 + tb0 + tt);
+        if (k < N) return to_f32<T>(xbc[t * C_ + inner + g * N + k]);
+        if (k < 2 * N) return to_f32<T>(xbc[t * C_ + inner + groups * N + g * N + (k - N)]);
+        if (k < 2 * N + SS_COLS) {
+            const int c = col0 + k - 2 * N;
+            return c < P ? to_f32<T>(xbc[t * C_ + h * P + c]) : 0.f;
         }
-        const float x = col_ok ? to_f32<T>(xbc[row + h * P + col]) : 0.f;
-        const float dt = softplusf_(to_f32<T>(proj[(size_t)(t0 + tt) * stride + dt_off + h]) + bias);
-        const float decay = expf(a * dt), dx = dt * x;
-        __syncthreads();
-        float acc = 0.f;
+        return to_f32<T>(proj[t * stride + dt_off + h]);
+    };
+    auto put = [&](float* buf, int e, float v) {
+        const int tt = e / ROW, k = e - tt * ROW;
+        if (k < ROW - 1) {
+            buf[tt * ROWS + k] = v;
+        } else {
+            const float dt = softplusf_(v + bias);
+            buf[tt * ROWS + ROW - 1] = expf(a * dt);
+            buf[tt * ROWS + ROW] = dt;
+        }
+    };
+    const int n_batches = (n + SS_TB - 1) / SS_TB;
 #pragma unroll
-        for (int j = 0; j < NR; ++j) {
-            if (j < rows) {
-                const int i = part + SS_PARTS * j;
-                if (i < N) {
-                    s[j] = fmaf(decay, s[j], Bb[i] * dx);
-                    acc = fmaf(s[j], Cb[i], acc);
-                }
+    for (int i = 0; i < PF; ++i) {
+        const int e = tid + NT * i;
+        if (e < EB) put(sm, e, fetch(e, 0, min(SS_TB, n)));
+    }
+    __syncthreads();
+    for (int b = 0; b < n_batches; ++b) {
+        const float* cur = sm + (b & 1) * SS_TB * ROWS;
+        float* nxt = sm + ((b + 1) & 1) * SS_TB * ROWS;
+        const bool more = b + 1 < n_batches;
+        float pf[PF];
+        if (more) {
+            const int nb2 = min(SS_TB, n - (b + 1) * SS_TB);
+#pragma unroll
+            for (int i = 0; i < PF; ++i) {
+                const int e = tid + NT * i;
+                pf[i] = e < EB ? fetch(e, (b + 1) * SS_TB, nb2) : 0.f;
             }
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-        if (part == 0 && col_ok) y[(size_t)(t0 + tt) * inner + h * P + col] = acc + dskip * x;
+        const int nb = min(SS_TB, n - b * SS_TB);
+        for (int tt = 0; tt < nb; ++tt) {
+            const float* Bb = cur + tt * ROWS;
+            const float* Cb = Bb + N;
+            const float x = Bb[2 * N + (tid >> 3)], decay = Bb[ROW - 1], dx = Bb[ROW] * x;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < NR; ++j) {
+                if (j < rows) {
+                    const int i = part + SS_PARTS * j;
+                    if (i < N) {
+                        s[j] = fmaf(decay, s[j], Bb[i] * dx);
+                        acc = fmaf(s[j], Cb[i], acc);
+                    }
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (part == 0 && col_ok) y[(size_t)(t0 + b * SS_TB + tt) * inner + h * P + col] = acc + dskip * x;
+        }
+        if (more) {
+#pragma unroll
+            for (int i = 0; i < PF; ++i) {
+                const int e = tid + NT * i;
+                if (e < EB) put(nxt, e, pf[i]);
+            }
+        }
+        __syncthreads();
     }
 #pragma unroll
     for (int j = 0; j < NR; ++j) {
@@ -579,10 +1032,16 @@ MSGL_API int msgl_ssm_scan(const void* xbc, int heads, int groups, int N, int P,
     if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || N > SS_PARTS * SS_MAX_ROWS) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     const dim3 grid(B, heads, (P + SS_COLS - 1) / SS_COLS);
-    const size_t smem = (size_t)4 * N * sizeof(float);
+    const size_t smem = (size_t)2 * SS_TB * (2 * N + SS_COLS + 2) * sizeof(float);
     const int nr = (N + SS_PARTS - 1) / SS_PARTS;
 #define SS_LAUNCH(NRR)                                                                                                          \
     do {                                                                                                                        \
+        static MsglOncePerDevice once;                                                                                          \
+        if (smem > 48 * 1024 && once.due()) {                                                                                   \
+            cudaFuncSetAttribute(ssm_scan_kernel<float, NRR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);         \
+            cudaFuncSetAttribute(ssm_scan_kernel<__nv_bfloat16, NRR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+            once.mark();                                                                                                        \
+        }                                                                                                                       \
         if (dtype == MSGL_F32)                                                                                                  \
             ssm_scan_kernel<float, NRR><<<grid, SS_COLS * SS_PARTS, smem, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias, \
                                                                                   A_log, Dskip, state, q_start, slots, y);      \

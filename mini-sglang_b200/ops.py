@@ -1043,6 +1043,9 @@ _gated = None
 ACT_RELU2, ACT_RELU = 3, 4
 SIGMOID_ATTENTION_ROWS = 8          # (token, head) rows of a block of the sigmoid attention kernel
 SIGMOID_ATTENTION_MAX_HEAD_DIM = 512
+MINGRU_CHUNK = 32                   # tokens of a chunk when a long portion's recurrence runs in chunks side by side
+SIGMOID_ATTENTION_MMA_ROWS = 64     # rows of a block of the tensor-core kernel
+SIGMOID_ATTENTION_MMA_MAX_HEAD_DIM = 128
 SIGMOID_ATTENTION_SPLIT_KEYS = 256  # keys of a piece when a one-token step cuts a request's keys over several blocks
 SSM_MAX_STATE = 512
 ROUTE_MAX_EXPERTS, ROUTE_MAX_GROUPS = 1024, 64
@@ -1058,7 +1061,11 @@ def _gated_lib():
             [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p]
         lib.msgl_sigmoid_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p] + \
             [c_int] * 11 + [c_float, c_int, c_void_p]
+        lib.msgl_sigmoid_attention_mma.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p] + \
+            [c_int] * 9 + [c_float, c_void_p]
         lib.msgl_mingru.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int] + [c_void_p] * 6 + [c_ll, c_float, c_int, c_int, c_void_p]
+        lib.msgl_mingru_chunked.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int] + [c_void_p] * 6 + [c_ll, c_float, c_int, c_int, c_int,
+                                            c_void_p, c_void_p, c_int, c_void_p]
         lib.msgl_pair_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_void_p]
         lib.msgl_causal_conv_act.argtypes = [c_void_p, c_ll, c_int, c_int, c_int] + [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_ssm_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int] + [c_void_p] * 7 + [c_int, c_int, c_void_p]
@@ -1122,29 +1129,39 @@ def headnorm_kvwrite(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor,
     return q_out
 
 
-def sigmoid_attention_geometry(n_q: int, n_kv: int) -> Tuple[int, int]:
-    """(tokens per query tile, query heads of one kv head per block) of the sigmoid attention kernel."""
+def sigmoid_attention_geometry(n_q: int, n_kv: int, tensor_cores: bool = False) -> Tuple[int, int]:
+    """(tokens per query tile, query heads of one kv head per block) of the sigmoid attention kernels."""
     G = n_q // n_kv
-    gh = min(G, SIGMOID_ATTENTION_ROWS)
-    return SIGMOID_ATTENTION_ROWS // gh, gh
+    rows = SIGMOID_ATTENTION_MMA_ROWS if tensor_cores else SIGMOID_ATTENTION_ROWS
+    gh = min(G, rows)
+    return rows // gh, gh
+
+
+def sigmoid_attention_on_tensor_cores(dtype: torch.dtype, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel takes these rows: bfloat16, head sizes in steps of 8 up to 128."""
+    return dtype == torch.bfloat16 and d % 8 == 0 and dv % 8 == 0 and max(d, dv) <= SIGMOID_ATTENTION_MMA_MAX_HEAD_DIM
 
 
 def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, q_start: torch.Tensor,
                       kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int, scale: float, bias: torch.Tensor,
-                      q_lens: Optional[Sequence[int]], workspace=None) -> None:
+                      q_lens: Optional[Sequence[int]], workspace=None, tensor_cores: Optional[bool] = None) -> None:
     """Causal attention over the paged cache whose weight of key j for the query at position i is sigmoid(q . k * scale +
     bias[head][min(i - j, L - 1)]), each key by itself (nothing is normed over the keys).  q [T, heads, d]; K cache [pages, n_kv,
     page, d], V cache [pages, n_kv, page, dv]; bias float32 [heads, L]; out [T, heads * dv] (may be a view into packed rows).
     q_lens: the requests' numbers of tokens as the host knows them (they size the launch), or None when every request brings one
     token: the keys are then cut into pieces of SIGMOID_ATTENTION_SPLIT_KEYS for as many blocks as the block table's width asks
-    for, whose sums are added in order (workspace: a parts.Workspace for the pieces)."""
+    for, whose sums are added in order (workspace: a parts.Workspace for the pieces).  tensor_cores: None = the bfloat16 kernel
+    with mma products where it takes the sizes (`sigmoid_attention_on_tensor_cores`), the float32 one elsewhere; False = the float32
+    arithmetic kernel in any case."""
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, bias)
     T, n_q, d = q.shape
     dv = v_cache.shape[3]
     assert q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
     out_stride = _rows_view(out, n_q * dv, "out")
     B = kv_len.numel()
-    QT, GH = sigmoid_attention_geometry(n_q, n_kv)
+    if tensor_cores is None:
+        tensor_cores = sigmoid_attention_on_tensor_cores(q.dtype, d, dv) and out_stride % 2 == 0 and out.data_ptr() % 4 == 0
+    QT, GH = sigmoid_attention_geometry(n_q, n_kv, tensor_cores)
     assert bias.dtype == torch.float32 and bias.dim() == 2 and bias.shape[0] == n_q and bias.is_contiguous()
     uniform = q_lens is None
     n_tiles = B if uniform else sum(-(-n // QT) for n in q_lens)
@@ -1155,10 +1172,16 @@ def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
             numel = splits * T * n_q * dv
             part = workspace.get("sigmoid_attention_pieces", numel, torch.float32) if workspace is not None else \
                 torch.empty(numel, dtype=torch.float32, device=q.device)
-    code = _gated_lib().msgl_sigmoid_attention(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
-        n_tiles, _ptr(bias), bias.shape[1], _ptr(out), out_stride, _ptr(part), splits, SIGMOID_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv,
-        d, dv, page_size, QT, GH, float(scale), _dt(q), _stream())
+    if tensor_cores:
+        code = _gated_lib().msgl_sigmoid_attention_mma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+            n_tiles, _ptr(bias), bias.shape[1], _ptr(out), out_stride, _ptr(part), splits, SIGMOID_ATTENTION_SPLIT_KEYS, T, B, n_q,
+            n_kv, d, dv, page_size, float(scale), _stream())
+    else:
+        code = _gated_lib().msgl_sigmoid_attention(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+            n_tiles, _ptr(bias), bias.shape[1], _ptr(out), out_stride, _ptr(part), splits, SIGMOID_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv,
+            d, dv, page_size, QT, GH, float(scale), _dt(q), _stream())
     _check(code, f"sigmoid_attention (head sizes {d}, {dv})")
     if splits > 1:
         global LAUNCHES
@@ -1166,10 +1189,13 @@ def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 
 def mingru(z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, z_bias: torch.Tensor, x_bias: torch.Tensor, *, state: torch.Tensor,
-           q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+           q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, scale: float = 1.0, q_lens: Optional[Sequence[int]] = None,
+           workspace=None) -> None:
     """A gated recurrence per channel over the step's tokens, continued from and written back to `state` [slots, W] float32:
     zz = sigmoid(z + z_bias), a = x + x_bias, c = a + 1/2 where a >= 0 and sigmoid(a) below, S <- (1 - zz) S + zz c;
-    out = S * silu(g) * scale.  z, x, g [T, W]: views into one packed projection; out [T, W] (may be a view)."""
+    out = S * silu(g) * scale.  z, x, g [T, W]: views into one packed projection; out [T, W] (may be a view).  q_lens: the
+    requests' numbers of tokens as the host knows them; with a request of 2 * MINGRU_CHUNK tokens or more the tokens run in chunks
+    side by side (same sums in float32, another order), else one by one."""
     _need_cuda(z, x, g, z_bias, x_bias, state, q_start, slots, out)
     T, W = z.shape
     stride = _rows_view(z, W, "z")
@@ -1177,6 +1203,19 @@ def mingru(z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, z_bias: torch.Tens
     assert z_bias.dtype == torch.float32 and x_bias.dtype == torch.float32 and z_bias.numel() == W and x_bias.numel() == W
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (W,)
     B = q_start.numel() - 1
+    if q_lens is not None and max(q_lens, default=0) >= 2 * MINGRU_CHUNK:
+        L = MINGRU_CHUNK
+        n_chunks = sum(-(-n // L) for n in q_lens)
+        numel = (2 * n_chunks + B) * W
+        buf = workspace.get("mingru_chunks", numel, torch.float32) if workspace is not None else \
+            torch.empty(numel, dtype=torch.float32, device=z.device)
+        code = _gated_lib().msgl_mingru_chunked(_ptr(z), stride, 0, _col_off(x, z), _col_off(g, z), W, _ptr(z_bias), _ptr(x_bias), _ptr(state),
+                                                _ptr(q_start), _ptr(slots), _ptr(out), _rows_view(out, W, "out"), float(scale), B, L,
+                                                n_chunks, _ptr(buf), _ptr(buf[2 * n_chunks * W:]), _dt(z), _stream())
+        _check(code, "mingru (chunks)")
+        global LAUNCHES
+        LAUNCHES += 1
+        return
     code = _gated_lib().msgl_mingru(_ptr(z), stride, 0, _col_off(x, z), _col_off(g, z), W, _ptr(z_bias), _ptr(x_bias), _ptr(state),
                                     _ptr(q_start), _ptr(slots), _ptr(out), _rows_view(out, W, "out"), float(scale), B, _dt(z), _stream())
     _check(code, "mingru")

@@ -55,7 +55,8 @@ class MinGRU(Mixer, Projected):
     def middle(self, proj, act, ctx, cache=None, writes_cache=True, out_scale=1.0):
         W = self.W
         ops.mingru(proj[:, :W], proj[:, W:2 * W], proj[:, 2 * W:3 * W], self.z_bias, self.x_bias, state=cache.state,
-                   q_start=ctx.q_start, slots=ctx.slots, out=act, scale=out_scale)
+                   q_start=ctx.q_start, slots=ctx.slots, out=act, scale=out_scale,
+                   q_lens=None if ctx.uniform_decode else ctx.host_q_lens, workspace=ctx.workspace)
 
     def forward(self, x, ctx, cache, writes_cache: bool = True):
         return self.forward_projected(x, ctx, cache, writes_cache)

@@ -134,10 +134,12 @@ def dense_ff(u, w, p: str):
     return torch.relu(u @ w[p + ".up"].T) ** 2 @ w[p + ".down"].T
 
 
-def route(u, w, p: str, r: dict):
+def route(u, w, p: str, r: dict, margins: Optional[list] = None):
     """-> (chosen experts [T, top], their weights [T, top]).  Scores are sigmoids of the router's logits; the choice adds a
     correction per expert and is limited to the best groups (a group counts by the sum of its two largest choice scores; experts
-    of other groups are out, whatever their sign); the weights are the chosen experts' own scores over their sum."""
+    of other groups are out, whatever their sign); the weights are the chosen experts' own scores over their sum.  `margins`, if
+    given, receives [T]: by how much the choice was made, the smaller of the gap between the last kept group and the first one left
+    out and the gap between the last chosen expert and the first allowed one left out."""
     s = torch.sigmoid(u.float() @ w[p + ".router"].float().T)
     choice = s + w[p + ".correction"].float()
     T, E = s.shape
@@ -150,12 +152,21 @@ def route(u, w, p: str, r: dict):
     allowed.scatter_(1, best, True)
     masked = torch.where(allowed[:, :, None].expand(T, gc, per).reshape(T, E), choice, torch.full_like(choice, -math.inf))
     idx = masked.topk(r["top"], dim=-1).indices
+    if margins is not None:
+        gap = torch.full((T,), math.inf)
+        if keep < gc:
+            g = gscore.sort(dim=-1, descending=True).values
+            gap = g[:, keep - 1] - g[:, keep]
+        if r["top"] < keep * per:
+            c = masked.sort(dim=-1, descending=True).values
+            gap = torch.minimum(gap, c[:, r["top"] - 1] - c[:, r["top"]])
+        margins.append(gap)
     wts = s.gather(1, idx)
     return idx, wts / (wts.sum(dim=-1, keepdim=True) + 1e-20)
 
 
-def moe_ff(u, w, p: str, m: dict):
-    idx, wts = route(u, w, p, m["router"])
+def moe_ff(u, w, p: str, m: dict, margins: Optional[list] = None):
+    idx, wts = route(u, w, p, m["router"], margins)
     out = torch.zeros_like(u)
     for t in range(u.shape[0]):
         for e, a in zip(idx[t].tolist(), wts[t]):
@@ -165,8 +176,9 @@ def moe_ff(u, w, p: str, m: dict):
 
 
 def forward_sequence(config: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float32,
-                     streams: Optional[list] = None) -> torch.Tensor:
-    """-> logits [T, vocab].  `streams`, if given, receives the residual stream after every run of a layer."""
+                     streams: Optional[list] = None, margins: Optional[list] = None) -> torch.Tensor:
+    """-> logits [T, vocab].  `streams`, if given, receives the residual stream after every run of a layer; `margins` one [T] per
+    routed feed-forward run (see `route`)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps, m = config["norm"]["eps"], config.get("residual_mult", 1.0)
     if len(tokens) > config["max_positions"]:
@@ -189,7 +201,7 @@ def forward_sequence(config: dict, w: Dict[str, torch.Tensor], tokens: List[int]
             if layer["mlp"]["kind"] == "dense":
                 x = x + m * dense_ff(u, w, p + ".mlp")
             else:
-                x = x + m * moe_ff(u, w, p + ".mlp", layer["mlp"])
+                x = x + m * moe_ff(u, w, p + ".mlp", layer["mlp"], margins)
         if streams is not None:
             streams.append(x.clone())
     return dynamic_tanh(x, w, "final.norm") @ w["head"].T

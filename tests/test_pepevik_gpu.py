@@ -44,9 +44,20 @@ def model_dir(name):
 
 
 @functools.lru_cache(None)
-def plain(name, tokens):
+def _plain_run(name, tokens):
+    margins = []
     with torch.no_grad():
-        return pp.forward_sequence(CONFIGS_P[name], weights(name), list(tokens)).float()
+        logits = pp.forward_sequence(CONFIGS_P[name], weights(name), list(tokens), margins=margins).float()
+    return logits, (torch.stack(margins).amin(dim=0) if margins else torch.full((len(tokens),), math.inf))
+
+
+def plain(name, tokens):
+    return _plain_run(name, tokens)[0]
+
+
+def close_call(name, tokens, pos):
+    """Whether a router of the plain run chose at this position by less than the rounding of its bfloat16 input can move a score."""
+    return float(_plain_run(name, tokens)[1][pos]) < CLOSE_CALL
 
 
 def runner(name, dtype, num_pages, max_reqs=4, page_size=None, graphs=True):
@@ -61,6 +72,7 @@ def runner(name, dtype, num_pages, max_reqs=4, page_size=None, graphs=True):
 # near 1 % of a row's rms at these widths.  The bound is 3 %; the faults it is meant to catch move the rows by 3.5 % or more
 # (tests/test_pepevik_cpu.py), and the float32 run of the same schedule holds the logic to 1e-4.
 BF16_RMS_FRACTION_P = 0.03
+CLOSE_CALL = 0.005          # difference of two choice scores (sigmoids plus corrections) below which bfloat16 may choose otherwise
 
 
 def row_close(row, want, dtype, bound=BF16_RMS_FRACTION_P):
@@ -76,9 +88,11 @@ def row_close(row, want, dtype, bound=BF16_RMS_FRACTION_P):
 
 
 def compare(name, dtype, got, seqs, ref=None, bound=BF16_RMS_FRACTION_P):
-    """Every row against the plain implementation.  bfloat16: rounding noise has outliers (a token whose router scores are a
-    close call, a row whose sums nearly cancel before a norm), so one row in fifty (at least one) may pass the bound, none by more
-    than two and a half times; a fault of the cache or of a state moves every row behind it by more than that."""
+    """Every row against the plain implementation.  bfloat16: rounding noise has outliers (a row whose sums nearly cancel before a
+    norm), so one row in fifty (at least one) may pass the bound, none by more than two and a half times; a fault of the cache or
+    of a state moves every row behind it by more than that.  A position at which a router of the plain run chose by less than
+    CLOSE_CALL may run another expert in bfloat16 (with one expert a token that replaces the whole feed-forward output, measured
+    up to 11 % of the row's rms): such a row is held to five times the bound and counts with neither group."""
     assert got
     over = []
     for (rid, pos), row in sorted(got.items()):
@@ -87,9 +101,11 @@ def compare(name, dtype, got, seqs, ref=None, bound=BF16_RMS_FRACTION_P):
             row_close(row, want, dtype, bound)
         except AssertionError as e:
             if dtype == "bfloat16" and torch.isfinite(row).all():
+                close = ref is None and close_call(name, tuple(seqs[rid]), pos)
                 try:
-                    row_close(row, want, dtype, 2.5 * bound)
-                    over.append((rid, pos))
+                    row_close(row, want, dtype, (5.0 if close else 2.5) * bound)
+                    if not close:
+                        over.append((rid, pos))
                     continue
                 except AssertionError:
                     pass
@@ -198,7 +214,7 @@ def test_head_norms_query_factor_and_cache_rows(dtype, geo):
 # ---------------------------------------------------------------------------------------------------------------------
 # sigmoid attention: every key stands by itself, so ONE key is made to take a weight of nearly 1 among keys of weight nearly 0
 # ---------------------------------------------------------------------------------------------------------------------
-def _sigmoid_case(dtype, *, H, G, d, dv, P, ctx, n_new, spike, seed, wide_table=0, L_bias=None):
+def _sigmoid_case(dtype, *, H, G, d, dv, P, ctx, n_new, spike, seed, wide_table=0, L_bias=None, tensor_cores=None):
     """`ctx` tokens lie in the cache, `n_new` more are the step's; the key at absolute position `spike` (negative: none) points
     the way every query points, all other scores sit near -14.  Returns the expected output [n_new, H, dv] (float64 sums over
     the numbers the kernel reads).  L_bias: the bias table's length (distances beyond it take its last entry)."""
@@ -238,17 +254,26 @@ def _sigmoid_case(dtype, *, H, G, d, dv, P, ctx, n_new, spike, seed, wide_table=
     kc[0], vc[0] = 0, 0
     out = torch.full((n_new, H * dv + 8), float("nan"), dtype=dt).cuda()
     ops.sigmoid_attention(q.cuda(), out[:, 8:], kc.cuda(), vc.cuda(), q_start=i32([0, n_new]), kv_len=i32([L]), block_table=table.cuda(),
-                          n_kv=G, page_size=P, scale=1.0, bias=bias.cuda(), q_lens=None if n_new == 1 else [n_new])
+                          n_kv=G, page_size=P, scale=1.0, bias=bias.cuda(), q_lens=None if n_new == 1 else [n_new], tensor_cores=tensor_cores)
     got = out[:, 8:].float().cpu().view(n_new, H, dv)
     assert torch.isfinite(got).all() and torch.isnan(out[:, :8]).all()
     torch.testing.assert_close(got, want.float(), **tol_of(dtype, 2e-5, 4e-2))
     return want
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n_new", [1, 2, 13])
-def test_sigmoid_attention_sees_every_earlier_key_and_no_later_one(dtype, n_new):
-    geo = dict(H=6, G=3, d=24, dv=40, P=4, ctx=300, n_new=n_new, seed=21)
+# "bfloat16" takes the tensor-core kernel where it serves the head sizes, "bfloat16 plain" the float32-arithmetic kernel always
+SIGMOID_KERNELS = ["float32", "bfloat16", "bfloat16 plain"]
+
+
+def _kernel_of(which):
+    return ("bfloat16", False) if which == "bfloat16 plain" else (which, None)
+
+
+@pytest.mark.parametrize("which", SIGMOID_KERNELS)
+@pytest.mark.parametrize("n_new", [1, 2, 13, 70])
+def test_sigmoid_attention_sees_every_earlier_key_and_no_later_one(which, n_new):
+    dtype, tc = _kernel_of(which)
+    geo = dict(H=6, G=3, d=24, dv=40, P=4, ctx=300, n_new=n_new, seed=21, tensor_cores=tc)
     last = {}
     for name, spike in (("none", -1), ("first", 0), ("second", 1), ("far", 37), ("page end", 3), ("page start", 4), ("chunk edge", 31),
                         ("next chunk", 32), ("just before", 299), ("own", 300 + n_new - 1), ("piece edge", 255), ("next piece", 256)):
@@ -265,8 +290,11 @@ def test_sigmoid_attention_sees_every_earlier_key_and_no_later_one(dtype, n_new)
         assert (w - none).abs().amin(dim=(1, 2)).min() > 1.0
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_sigmoid_attention_other_geometries(dtype):
+@pytest.mark.parametrize("which", SIGMOID_KERNELS)
+def test_sigmoid_attention_other_geometries(which):
+    import functools
+    dtype, tc = _kernel_of(which)
+    _sigmoid_case = functools.partial(globals()["_sigmoid_case"], tensor_cores=tc)
     # the first tokens of a sequence: nothing cached, one and two tokens, a long portion
     _sigmoid_case(dtype, H=2, G=1, d=40, dv=24, P=4, ctx=0, n_new=1, spike=0, seed=1)
     _sigmoid_case(dtype, H=2, G=1, d=40, dv=24, P=4, ctx=0, n_new=2, spike=1, seed=2)
@@ -286,6 +314,50 @@ def test_sigmoid_attention_other_geometries(dtype):
     _sigmoid_case(dtype, H=8, G=2, d=128, dv=128, P=16, ctx=200, n_new=150, spike=120, seed=10)
     # distances beyond the bias table take its last entry
     _sigmoid_case(dtype, H=2, G=1, d=16, dv=16, P=4, ctx=50, n_new=4, spike=2, seed=11, L_bias=20)
+    # more heads on a kv head than a block has rows; three heads (a block's rows are no whole number of tokens); a portion whose
+    # tiles end at, just before and just behind a tile of keys
+    _sigmoid_case(dtype, H=72, G=1, d=16, dv=24, P=8, ctx=100, n_new=3, spike=64, seed=12)
+    _sigmoid_case(dtype, H=3, G=1, d=8, dv=8, P=4, ctx=60, n_new=50, spike=63, seed=13)
+    for ctx, n_new, spike in ((0, 64, 63), (1, 63, 63), (1, 64, 64), (64, 64, 64), (63, 130, 127), (448, 128, 511)):
+        _sigmoid_case(dtype, H=4, G=2, d=64, dv=64, P=16, ctx=ctx, n_new=n_new, spike=spike, seed=14)
+
+
+@pytest.mark.parametrize("which", SIGMOID_KERNELS)
+def test_sigmoid_attention_of_a_batch_equals_each_request_alone(which):
+    """Portions of unequal requests and single tokens in one launch: every row equals, bit for bit, the launch of its request alone."""
+    from mini_sglang_b200 import ops
+    dtype, tc = _kernel_of(which)
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(5)
+    H, G, d, dv, P = 8, 2, 32, 48, 8
+    ctxs, news = [130, 0, 77, 511, 64], [1, 67, 5, 1, 32]
+    T = sum(news)
+    n_pages = sum(-(-(c + n) // P) for c, n in zip(ctxs, news))
+    kc = (0.3 * torch.randn(n_pages + 1, G, P, d, generator=g)).to(dt).cuda()
+    vc = torch.randn(n_pages + 1, G, P, dv, generator=g).to(dt).cuda()
+    q = torch.randn(T, H, d, generator=g).to(dt).cuda()
+    bias = (-2.0 - torch.log1p(0.3 * torch.arange(700.0))[None, :] * torch.rand(H, 1, generator=g)).float().contiguous().cuda()
+    order = torch.randperm(n_pages, generator=g) + 1
+    width = max(-(-(c + n) // P) for c, n in zip(ctxs, news))
+    table = torch.zeros(len(ctxs), width, dtype=torch.int32)
+    at = 0
+    for r, (c, n) in enumerate(zip(ctxs, news)):
+        k = -(-(c + n) // P)
+        table[r, :k] = order[at:at + k].to(torch.int32)
+        at += k
+    table = table.cuda()
+    starts = [0]
+    for n in news:
+        starts.append(starts[-1] + n)
+    out = torch.zeros(T, H * dv, dtype=dt).cuda()
+    ops.sigmoid_attention(q, out, kc, vc, q_start=i32(starts), kv_len=i32([c + n for c, n in zip(ctxs, news)]), block_table=table, n_kv=G,
+                          page_size=P, scale=0.2, bias=bias, q_lens=news, tensor_cores=tc)
+    assert torch.isfinite(out).all() and float(out.abs().max()) > 0
+    for r, (c, n) in enumerate(zip(ctxs, news)):
+        alone = torch.zeros(n, H * dv, dtype=dt).cuda()
+        ops.sigmoid_attention(q[starts[r]:starts[r + 1]].contiguous(), alone, kc, vc, q_start=i32([0, n]), kv_len=i32([c + n]),
+                              block_table=table[r:r + 1].contiguous(), n_kv=G, page_size=P, scale=0.2, bias=bias, q_lens=[n], tensor_cores=tc)
+        assert torch.equal(alone, out[starts[r]:starts[r + 1]]), r
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -310,13 +382,16 @@ def _shared_steps(lens, cuts, order, run):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("W", [5, 72, 300])
-def test_min_gru_in_portions_and_batches(dtype, W):
+@pytest.mark.parametrize("long", [False, True])
+def test_min_gru_in_portions_and_batches(dtype, W, long):
     """Three requests with states of their own in shared steps (ninety single tokens among them), gates from nearly closed to
-    nearly open, candidates on both sides of zero; a fourth request then takes a state row that was used before."""
+    nearly open, candidates on both sides of zero; a fourth request then takes a state row that was used before.  long: portions
+    that run in chunks side by side (whole chunks, a last chunk of one token, a short request beside a long one)."""
     from mini_sglang_b200 import ops
     g = torch.Generator().manual_seed(W)
     dt = DT[dtype]
-    lens = {0: 90, 1: 37, 2: 64}
+    lens = {0: 290, 1: 137, 2: 164} if long else {0: 90, 1: 37, 2: 64}
+    cuts = {0: [1] * 90 + [200], 1: [130, 2, 2, 3], 2: [5, 65, 1, 1, 92]} if long else {0: [1] * 90, 1: [30, 2, 2, 3], 2: [5, 40, 1, 1, 17]}
     u = {r: (3 * torch.randn(n, 3 * W + 5, generator=g)).to(dt) for r, n in lens.items()}
     zb, xb = 2 * torch.randn(W, generator=g), torch.randn(W, generator=g)
     state = torch.full((5, W), float("nan")).cuda()
@@ -326,7 +401,8 @@ def test_min_gru_in_portions_and_batches(dtype, W):
         x = torch.cat([u[r][a:a + n] for r, a, n in zip(reqs, starts, ns)]).cuda()
         out = torch.full((x.shape[0], W + 3), float("nan"), dtype=dt).cuda()
         ops.mingru(x[:, 2:2 + W], x[:, 2 + W:2 + 2 * W], x[:, 2 + 2 * W:2 + 3 * W], zb.cuda(), xb.cuda(), state=state,
-                   q_start=i32(np.concatenate(([0], np.cumsum(ns))).tolist()), slots=i32([r + 1 for r in reqs]), out=out[:, 3:], scale=0.7)
+                   q_start=i32(np.concatenate(([0], np.cumsum(ns))).tolist()), slots=i32([r + 1 for r in reqs]), out=out[:, 3:], scale=0.7,
+                   q_lens=list(ns) if long else None)
         assert torch.isnan(out[:, :3]).all()
         return out[:, 3:]
 
@@ -340,7 +416,7 @@ def test_min_gru_in_portions_and_batches(dtype, W):
             rows.append(S * pp.silu(gate[t]) * 0.7)
         return torch.stack(rows).float()
 
-    got = _shared_steps(lens, {0: [1] * 90, 1: [30, 2, 2, 3], 2: [5, 40, 1, 1, 17]}, (2, 0, 1), run)
+    got = _shared_steps(lens, cuts, (2, 0, 1), run)
     for r in lens:
         torch.testing.assert_close(got[r], want(u[r]), **tol_of(dtype, 2e-5, 2e-2))
     state[2].zero_()                                       # the row of request 1, handed to a new request
