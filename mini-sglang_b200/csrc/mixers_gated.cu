@@ -37,6 +37,47 @@ __device__ __forceinline__ float gelu_tanhf_(float z) {
 // ln(1 + e^x) without a threshold: max(x, 0) + ln(1 + e^-|x|)
 __device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
+// 16 bytes of activations at once: VecOf<T>::N elements to and from float (the address is 16-byte aligned)
+template <typename T> struct VecOf;
+template <> struct VecOf<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* o) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* o) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+};
+template <> struct VecOf<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const unsigned u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(u[i] << 16);
+            o[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* o) {
+        unsigned u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+            u[i] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(u[0], u[1], u[2], u[3]);
+    }
+};
+__device__ __forceinline__ float act_of(int act, float v) {
+    switch (act) {
+        case 0: return siluf_(v);
+        case 1: return gelu_tanhf_(v);
+        case 2: return sigmoidf_(v);
+        case 3: return v > 0.f ? v * v : 0.f;
+        default: return fmaxf(v, 0.f);
+    }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
@@ -713,7 +754,7 @@ MSGL_API int msgl_mingru(const void* proj, long long stride, int z_off, int x_of
 // the chunk and writes the outputs; the last chunk of a request writes the state back.  Float32 throughout; the result differs
 // from the token-by-token kernel by rounding only.  Block y = chunk (over all requests, in order), thread = channel.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ bool mingru_find_chunk(const int* __restrict__ q_start, int B, int L, int* sh, int& req, int& first, int& c0) {
+__device__ __forceinline__ bool find_chunk_y(const int* __restrict__ q_start, int B, int L, int* sh, int& req, int& first, int& c0) {
     if (threadIdx.x == 0) {
         int left = blockIdx.y, found = -1, base = 0;
         for (int r = 0; r < B; ++r) {
@@ -734,7 +775,7 @@ __global__ void mingru_chunk_sum_kernel(const void* proj_, long long stride, int
                                         const int* __restrict__ slots, int B, int L, float* __restrict__ sums, float* __restrict__ init) {
     __shared__ int sh[3];
     int r, first, ci;
-    if (!mingru_find_chunk(q_start, B, L, sh, r, first, ci)) return;
+    if (!find_chunk_y(q_start, B, L, sh, r, first, ci)) return;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= W) return;
     if (ci == 0) init[(size_t)r * W + c] = state[(size_t)slots[r] * W + c];
@@ -761,7 +802,7 @@ __global__ void mingru_chunk_out_kernel(const void* proj_, long long stride, int
                                         float c_out) {
     __shared__ int sh[3];
     int r, first, ci;
-    if (!mingru_find_chunk(q_start, B, L, sh, r, first, ci)) return;
+    if (!find_chunk_y(q_start, B, L, sh, r, first, ci)) return;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= W) return;
     float S = init[(size_t)r * W + c];
@@ -865,6 +906,65 @@ __global__ void causal_conv_act_kernel(const void* in_, long long stride, int of
     reinterpret_cast<T*>(out_)[(size_t)t * C + c] = from_f32<T>(acc);
 }
 
+// The same with 16 bytes of channels a thread and CV_TB tokens in turn, for up to 4 taps: the request's last three inputs stay in
+// registers from token to token.  A tap that does not exist (fewer than 4) has weight 0 and is not read; the sum of a token is the
+// same sequence of multiply-adds as above.
+#define CV_TB 8
+template <typename T>
+__global__ void __launch_bounds__(128)
+causal_conv_act_vec_kernel(const void* in_, long long stride, int off, int C, int K, const float* __restrict__ w, const float* __restrict__ bias,
+                           const void* state_, const int* __restrict__ token_req, const int* __restrict__ q_start,
+                           const int* __restrict__ slots, void* out_, int act, int T_) {
+    constexpr int V = VecOf<T>::N;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (c >= C) return;
+    const T* in = reinterpret_cast<const T*>(in_) + off + c;
+    const T* state = reinterpret_cast<const T*>(state_);
+    T* out = reinterpret_cast<T*>(out_) + c;
+    const int skip = 4 - K;
+    float wv[4][V], bv[V], win[3][V];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < V; ++i) wv[j][i] = j >= skip ? w[(size_t)(j - skip) * C + c + i] : 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) bv[i] = bias ? bias[c + i] : 0.f;
+    int prev = -1;
+    for (int tt = 0; tt < CV_TB; ++tt) {
+        const int t = blockIdx.y * CV_TB + tt;
+        if (t >= T_) break;
+        const int r = token_req[t];
+        if (r != prev) {                                 // the window of the request's inputs before t
+            const int local = t - q_start[r], slot = slots[r];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int li = local - 3 + j;
+                if (j >= skip) {
+                    if (li >= 0) VecOf<T>::load(in + (size_t)(t - 3 + j) * stride, win[j]);
+                    else VecOf<T>::load(state + ((size_t)slot * (K - 1) + (K - 1 + li)) * C + c, win[j]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) win[j][i] = 0.f;
+                }
+            }
+            prev = r;
+        }
+        float cur[V], o[V];
+        VecOf<T>::load(in + (size_t)t * stride, cur);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float acc = bv[i];
+            acc = fmaf(wv[0][i], win[0][i], acc);
+            acc = fmaf(wv[1][i], win[1][i], acc);
+            acc = fmaf(wv[2][i], win[2][i], acc);
+            acc = fmaf(wv[3][i], cur[i], acc);
+            o[i] = act == 0 ? siluf_(acc) : acc;
+            win[0][i] = win[1][i]; win[1][i] = win[2][i]; win[2][i] = cur[i];
+        }
+        VecOf<T>::store(out + (size_t)t * C, o);
+    }
+}
+
 template <typename T>
 __global__ void conv_state_shift_kernel(const void* in_, long long stride, int off, int C, int K, void* state_,
                                         const int* __restrict__ q_start, const int* __restrict__ slots) {
@@ -888,9 +988,19 @@ MSGL_API int msgl_causal_conv_act(const void* in, long long stride, int off, int
     if (C <= 0 || K < 1 || K > CV_MAX_TAPS || (K > 1 && state == nullptr)) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     const int threads = 128;
-    const dim3 grid((C + threads - 1) / threads, T_);
-    if (dtype == MSGL_F32) causal_conv_act_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
-    else causal_conv_act_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
+    const int V = dtype == MSGL_F32 ? 4 : 8;
+    const size_t item = dtype == MSGL_F32 ? 4 : 2;
+    const bool vec = K <= 4 && C % V == 0 && stride % V == 0 && off % V == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                     ((uintptr_t)state % 16) == 0 && (stride * (long long)item) % 16 == 0;
+    if (vec) {
+        const dim3 grid((C / V + threads - 1) / threads, (T_ + CV_TB - 1) / CV_TB);
+        if (dtype == MSGL_F32) causal_conv_act_vec_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_);
+        else causal_conv_act_vec_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_);
+    } else {
+        const dim3 grid((C + threads - 1) / threads, T_);
+        if (dtype == MSGL_F32) causal_conv_act_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
+        else causal_conv_act_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
+    }
     int code = msgl_check_launch();
     if (code != MSGL_OK || K == 1) return code;
     const dim3 g2((C + threads - 1) / threads, B);
@@ -1059,6 +1169,304 @@ MSGL_API int msgl_ssm_scan(const void* xbc, int heads, int groups, int N, int P,
 }
 
 // ---------------------------------------------------------------------------------------
+// The state-space recurrence over long portions: the tokens of a request in chunks of SC_L that run side by side.  With
+// la_t = the sum of log decay over the chunk's tokens up to and including t (log decay = -exp(A_log) * step, never positive):
+//     S_t = exp(la_t) S_start + sum over j <= t of exp(la_t - la_j) step_j B_j x_j^T
+// so a chunk is  S_end = exp(la_end) S_start + U  with  U = sum over t of exp(la_end - la_t) step_t B_t x_t^T, and
+//     y_t = exp(la_t) S_start^T C_t + sum over j <= t of [exp(la_t - la_j) step_j (C_t . B_j)] x_j + D x_t.
+// Every exponent is <= 0.  ssm_chunk_state_kernel leaves U and exp(la_end) of every (chunk, head); ssm_chunk_carry_kernel walks
+// a request's chunks in order, replaces each U by the state at the chunk's start and writes the request's state back;
+// ssm_chunk_out_kernel forms the outputs.  Float32 throughout; the result differs from the token-by-token kernel by rounding only.
+// Grid: x = head * column tiles + column tile, y = chunk (over all requests, in order).
+// ---------------------------------------------------------------------------------------
+#define SC_L 64             // tokens of a chunk
+#define SC_PT 64            // value columns of a block
+#define SC_THREADS 256
+#define SC_LS (SC_L + 4)    // row stride of the chunk's weights
+
+// steps and running log decays of the chunk's n tokens (rows beyond n: step 0, the last token's sum)
+template <typename T>
+__device__ __forceinline__ void ssm_chunk_steps(const T* __restrict__ proj, long long stride, int col, int t0, int n, float bias, float a,
+                                                float* dts, float* las) {
+    const int tid = threadIdx.x;
+    if (tid < SC_L) dts[tid] = tid < n ? softplusf_(to_f32<T>(proj[(size_t)(t0 + tid) * stride + col]) + bias) : 0.f;
+    __syncthreads();
+    if (tid < 32) {
+        const float v0 = a * dts[2 * tid], v1 = v0 + a * dts[2 * tid + 1];
+        float run = v1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, run, d);
+            if (tid >= d) run += o;
+        }
+        float before = __shfl_up_sync(0xffffffffu, run, 1);
+        if (tid == 0) before = 0.f;
+        las[2 * tid] = before + v0;
+        las[2 * tid + 1] = before + v1;
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+ssm_chunk_state_kernel(const void* xbc_, int heads, int groups, int N, int P, const void* proj_, long long stride, int dt_off,
+                       const float* __restrict__ dt_bias, const float* __restrict__ A_log, const int* __restrict__ q_start, int B,
+                       float* __restrict__ U, float* __restrict__ Adec) {
+    extern __shared__ __align__(16) float sc_sm[];
+    __shared__ int sh[3];
+    __shared__ float dts[SC_L], las[SC_L], ws[SC_L];
+    int r, first, ci;
+    if (!find_chunk_y(q_start, B, SC_L, sh, r, first, ci)) return;
+    const int ptiles = (P + SC_PT - 1) / SC_PT;
+    const int h = blockIdx.x / ptiles, p0 = (blockIdx.x - h * ptiles) * SC_PT;
+    const int tid = threadIdx.x;
+    const int t0 = q_start[r] + ci * SC_L, n = min(SC_L, q_start[r + 1] - t0);
+    const int g = h / (heads / groups), inner = heads * P, C_ = inner + 2 * groups * N;
+    const int NP = (N + 7) & ~7, NS = NP + 4;
+    float* Bw = sc_sm;                   // [SC_L][NS]: B_t * exp(la_end - la_t) * step_t
+    float* xs = sc_sm + SC_L * NS;       // [SC_L][SC_PT]
+    const T* xbc = reinterpret_cast<const T*>(xbc_);
+    ssm_chunk_steps<T>(reinterpret_cast<const T*>(proj_), stride, dt_off + h, t0, n, dt_bias[h], -expf(A_log[h]), dts, las);
+    const float la_end = las[SC_L - 1];
+    if (tid < SC_L) ws[tid] = expf(la_end - las[tid]) * dts[tid];
+    __syncthreads();
+    for (int e = tid; e < SC_L * NP; e += SC_THREADS) {
+        const int t = e / NP, k = e - t * NP;
+        Bw[t * NS + k] = (t < n && k < N) ? to_f32<T>(xbc[(size_t)(t0 + t) * C_ + inner + g * N + k]) * ws[t] : 0.f;
+    }
+    for (int e = tid; e < SC_L * SC_PT; e += SC_THREADS) {
+        const int t = e / SC_PT, p = p0 + (e - t * SC_PT);
+        xs[e] = (t < n && p < P) ? to_f32<T>(xbc[(size_t)(t0 + t) * C_ + h * P + p]) : 0.f;
+    }
+    __syncthreads();
+    const int tn = tid >> 4, tp = tid & 15;
+    float* Uo = U + (((size_t)(first + ci) * heads + h) * N) * P;
+    const bool vec = (P & 3) == 0;
+    for (int nb = 0; nb < NP; nb += 128) {
+        const int n0 = nb + tn * 8;
+        if (n0 >= NP) continue;
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll 2
+        for (int t = 0; t < n; ++t) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + t * SC_PT + tp * 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(Bw + t * NS + n0);
+            const float4 b1 = *reinterpret_cast<const float4*>(Bw + t * NS + n0 + 4);
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                acc[i][0] = fmaf(bb[i], xv.x, acc[i][0]);
+                acc[i][1] = fmaf(bb[i], xv.y, acc[i][1]);
+                acc[i][2] = fmaf(bb[i], xv.z, acc[i][2]);
+                acc[i][3] = fmaf(bb[i], xv.w, acc[i][3]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int k = n0 + i, p = p0 + tp * 4;
+            if (k >= N || p >= P) continue;
+            float* o = Uo + (size_t)k * P + p;
+            if (vec) {
+                *reinterpret_cast<float4*>(o) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (p + q < P) o[q] = acc[i][q];
+            }
+        }
+    }
+    if (tid == 0 && p0 == 0) Adec[(size_t)(first + ci) * heads + h] = expf(la_end);
+}
+
+// U [chunk][head][N * P]: in, a chunk's own sum; out, the state at the chunk's start.  Thread = one state element of (request, head).
+__global__ void ssm_chunk_carry_kernel(int heads, int NPel, const int* __restrict__ q_start, const int* __restrict__ slots,
+                                       float* __restrict__ U, const float* __restrict__ Adec, float* __restrict__ state) {
+    const int r = blockIdx.z, h = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= NPel) return;
+    int first = 0;
+    for (int q = 0; q < r; ++q) first += (q_start[q + 1] - q_start[q] + SC_L - 1) / SC_L;
+    const int nc = (q_start[r + 1] - q_start[r] + SC_L - 1) / SC_L;
+    if (nc <= 0) return;
+    float* Sg = state + ((size_t)slots[r] * heads + h) * NPel + e;
+    float S = *Sg;
+    const size_t step = (size_t)heads * NPel;
+    size_t idx = ((size_t)first * heads + h) * NPel + e;
+    float own = U[idx];
+    for (int c = 0; c < nc; ++c) {
+        const float next = c + 1 < nc ? U[idx + step] : 0.f;
+        U[idx] = S;
+        S = fmaf(Adec[(size_t)(first + c) * heads + h], S, own);
+        own = next;
+        idx += step;
+    }
+    *Sg = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+ssm_chunk_out_kernel(const void* xbc_, int heads, int groups, int N, int P, const void* proj_, long long stride, int dt_off,
+                     const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dskip,
+                     const int* __restrict__ q_start, int B, const float* __restrict__ U, float* __restrict__ y) {
+    extern __shared__ __align__(16) float sc_sm[];
+    __shared__ int sh[3];
+    __shared__ float dts[SC_L], las[SC_L];
+    int r, first, ci;
+    if (!find_chunk_y(q_start, B, SC_L, sh, r, first, ci)) return;
+    const int ptiles = (P + SC_PT - 1) / SC_PT;
+    const int h = blockIdx.x / ptiles, p0 = (blockIdx.x - h * ptiles) * SC_PT;
+    const int tid = threadIdx.x;
+    const int t0 = q_start[r] + ci * SC_L, n = min(SC_L, q_start[r + 1] - t0);
+    const int g = h / (heads / groups), inner = heads * P, C_ = inner + 2 * groups * N;
+    const int NP = (N + 7) & ~7, NS = NP + 4;
+    float* Cs = sc_sm;                       // [SC_L][NS]
+    float* Bs = Cs + SC_L * NS;              // [SC_L][NS]
+    float* xs = Bs + SC_L * NS;              // [SC_L][SC_PT]
+    float* Ws = xs + SC_L * SC_PT;           // [SC_L][SC_LS]: weight of token j's x in token t's output
+    const T* xbc = reinterpret_cast<const T*>(xbc_);
+    ssm_chunk_steps<T>(reinterpret_cast<const T*>(proj_), stride, dt_off + h, t0, n, dt_bias[h], -expf(A_log[h]), dts, las);
+    for (int e = tid; e < SC_L * NP; e += SC_THREADS) {
+        const int t = e / NP, k = e - t * NP;
+        const bool ok = t < n && k < N;
+        const size_t at = (size_t)(t0 + t) * C_ + inner + g * N + k;
+        Bs[t * NS + k] = ok ? to_f32<T>(xbc[at]) : 0.f;
+        Cs[t * NS + k] = ok ? to_f32<T>(xbc[at + (size_t)groups * N]) : 0.f;
+    }
+    for (int e = tid; e < SC_L * SC_PT; e += SC_THREADS) {
+        const int t = e / SC_PT, p = p0 + (e - t * SC_PT);
+        xs[e] = (t < n && p < P) ? to_f32<T>(xbc[(size_t)(t0 + t) * C_ + h * P + p]) : 0.f;
+    }
+    __syncthreads();
+    const int ti = tid >> 4, tj = tid & 15;
+    {   // C_t . B_j for the 4 x 4 pairs t = ti + 16 a, j = tj + 16 b
+        float gacc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) gacc[a][0] = gacc[a][1] = gacc[a][2] = gacc[a][3] = 0.f;
+        for (int k = 0; k < NP; k += 4) {
+            float4 c[4], b[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                c[a] = *reinterpret_cast<const float4*>(Cs + (ti + 16 * a) * NS + k);
+                b[a] = *reinterpret_cast<const float4*>(Bs + (tj + 16 * a) * NS + k);
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int bq = 0; bq < 4; ++bq)
+                    gacc[a][bq] = fmaf(c[a].w, b[bq].w, fmaf(c[a].z, b[bq].z, fmaf(c[a].y, b[bq].y, fmaf(c[a].x, b[bq].x, gacc[a][bq]))));
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int bq = 0; bq < 4; ++bq) {
+                const int t = ti + 16 * a, j = tj + 16 * bq;
+                Ws[t * SC_LS + j] = (j <= t && t < n) ? gacc[a][bq] * (expf(las[t] - las[j]) * dts[j]) : 0.f;
+            }
+    }
+    __syncthreads();
+    const int tp = tj;
+    float acc[4][4], acs[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+        acs[a][0] = acs[a][1] = acs[a][2] = acs[a][3] = 0.f;
+    }
+#pragma unroll 2
+    for (int j = 0; j < n; ++j) {
+        const float4 xv = *reinterpret_cast<const float4*>(xs + j * SC_PT + tp * 4);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const float w = Ws[(ti + 16 * a) * SC_LS + j];
+            acc[a][0] = fmaf(w, xv.x, acc[a][0]);
+            acc[a][1] = fmaf(w, xv.y, acc[a][1]);
+            acc[a][2] = fmaf(w, xv.z, acc[a][2]);
+            acc[a][3] = fmaf(w, xv.w, acc[a][3]);
+        }
+    }
+    const float* S = U + (((size_t)(first + ci) * heads + h) * N) * P;     // the state at the chunk's start
+    const int pc = p0 + tp * 4;
+    const bool vec = (P & 3) == 0;
+    if (pc < P) {
+#pragma unroll 4
+        for (int k = 0; k < N; ++k) {
+            float4 sv;
+            if (vec) {
+                sv = *reinterpret_cast<const float4*>(S + (size_t)k * P + pc);
+            } else {
+                const float* sp = S + (size_t)k * P + pc;
+                sv.x = sp[0];
+                sv.y = pc + 1 < P ? sp[1] : 0.f;
+                sv.z = pc + 2 < P ? sp[2] : 0.f;
+                sv.w = pc + 3 < P ? sp[3] : 0.f;
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float c = Cs[(ti + 16 * a) * NS + k];
+                acs[a][0] = fmaf(c, sv.x, acs[a][0]);
+                acs[a][1] = fmaf(c, sv.y, acs[a][1]);
+                acs[a][2] = fmaf(c, sv.z, acs[a][2]);
+                acs[a][3] = fmaf(c, sv.w, acs[a][3]);
+            }
+        }
+        const float dskip = Dskip[h];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int t = ti + 16 * a;
+            if (t >= n) continue;
+            const float e = expf(las[t]);
+            float* o = y + (size_t)(t0 + t) * inner + h * P + pc;
+            const float* xr = xs + t * SC_PT + tp * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (pc + q < P) o[q] = fmaf(e, acs[a][q], acc[a][q]) + dskip * xr[q];
+        }
+    }
+}
+
+// n_chunks: the sum over the requests of ceil(tokens / SC_L); U: float32 [n_chunks][heads][N][P] (16-byte aligned); Adec: float32
+// [n_chunks][heads]
+MSGL_API int msgl_ssm_scan_chunked(const void* xbc, int heads, int groups, int N, int P, const void* proj, long long stride, int dt_off,
+                                   const float* dt_bias, const float* A_log, const float* Dskip, float* state, const int* q_start,
+                                   const int* slots, float* y, int B, int n_chunks, float* U, float* Adec, int dtype, cudaStream_t stream) {
+    if (B <= 0 || n_chunks <= 0) return MSGL_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || U == nullptr || Adec == nullptr || n_chunks > 65535 ||
+        B > 65535 || heads > 65535 || ((uintptr_t)U & 15))
+        return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int NS = ((N + 7) & ~7) + 4;
+    const size_t smem_state = (size_t)(SC_L * NS + SC_L * SC_PT) * sizeof(float);
+    const size_t smem_out = (size_t)(2 * SC_L * NS + SC_L * SC_PT + SC_L * SC_LS) * sizeof(float);
+    const size_t smem_max = 200 * 1024;
+    if (smem_out > smem_max) return MSGL_ERR_SIZE;
+    static MsglOncePerDevice once;
+    if (once.due()) {
+        cudaFuncSetAttribute(ssm_chunk_state_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaFuncSetAttribute(ssm_chunk_state_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaFuncSetAttribute(ssm_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        cudaFuncSetAttribute(ssm_chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
+        once.mark();
+    }
+    const int ptiles = (P + SC_PT - 1) / SC_PT;
+    const dim3 grid(heads * ptiles, n_chunks);
+    const int NPel = N * P;
+    const dim3 cgrid((NPel + 255) / 256, heads, B);
+    if (dtype == MSGL_F32) {
+        ssm_chunk_state_kernel<float><<<grid, SC_THREADS, smem_state, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias, A_log,
+                                                                              q_start, B, U, Adec);
+        ssm_chunk_carry_kernel<<<cgrid, 256, 0, stream>>>(heads, NPel, q_start, slots, U, Adec, state);
+        ssm_chunk_out_kernel<float><<<grid, SC_THREADS, smem_out, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias, A_log,
+                                                                          Dskip, q_start, B, U, y);
+    } else {
+        ssm_chunk_state_kernel<__nv_bfloat16><<<grid, SC_THREADS, smem_state, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias,
+                                                                                      A_log, q_start, B, U, Adec);
+        ssm_chunk_carry_kernel<<<cgrid, 256, 0, stream>>>(heads, NPel, q_start, slots, U, Adec, state);
+        ssm_chunk_out_kernel<__nv_bfloat16><<<grid, SC_THREADS, smem_out, stream>>>(xbc, heads, groups, N, P, proj, stride, dt_off, dt_bias,
+                                                                                  A_log, Dskip, q_start, B, U, y);
+    }
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
 // out = (y * silu(z)) / rms over each of `parts` equal parts of the row * w * c:  the gate comes BEFORE the norm
 //   y float32 [T, N] contiguous; z and out [T, N] views into packed rows of the activation type; w float32 [N]
 // One warp per (token, part).
@@ -1101,16 +1509,24 @@ template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ x, long long x_stride, T* __restrict__ out, long long out_stride, int N, int act, float c) {
     const size_t t = blockIdx.y;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x) {
-        const float v = to_f32<T>(x[t * x_stride + i]);
-        float a;
-        switch (act) {
-            case 0: a = siluf_(v); break;
-            case 1: a = gelu_tanhf_(v); break;
-            case 2: a = sigmoidf_(v); break;
-            case 3: a = v > 0.f ? v * v : 0.f; break;
-            default: a = fmaxf(v, 0.f); break;
-        }
-        out[t * out_stride + i] = from_f32<T>(a * c);
+        out[t * out_stride + i] = from_f32<T>(act_of(act, to_f32<T>(x[t * x_stride + i])) * c);
+    }
+}
+
+// 16 bytes a thread over the flattened [T, N / V] grid
+template <typename T>
+__global__ void __launch_bounds__(256) unary_act_vec_kernel(const T* __restrict__ x, long long x_stride, T* __restrict__ out,
+                                                            long long out_stride, int N, int act, float c, long long total) {
+    constexpr int V = VecOf<T>::N;
+    const int per = N / V;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / per;
+        const int i = (int)(e - t * per) * V;
+        float v[V];
+        VecOf<T>::load(x + t * x_stride + i, v);
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[k] = act_of(act, v[k]) * c;
+        VecOf<T>::store(out + t * out_stride + i, v);
     }
 }
 
@@ -1118,6 +1534,15 @@ MSGL_API int msgl_unary_act(const void* x, long long x_stride, void* out, long l
                             cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
     if (N <= 0 || act < 0 || act > 4) return MSGL_ERR_SIZE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    const int V = dtype == MSGL_F32 ? 4 : 8;
+    if (N % V == 0 && x_stride % V == 0 && out_stride % V == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const long long total = (long long)T_ * (N / V);
+        const int blocks = (int)min((total + 255) / 256, (long long)msgl_sm_count() * 16);
+        if (dtype == MSGL_F32) unary_act_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, x_stride, (float*)out, out_stride, N, act, c, total);
+        else unary_act_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, N, act, c, total);
+        return msgl_check_launch();
+    }
     const dim3 grid(max(1, min((N + 255) / 256, 64)), T_);
     if (dtype == MSGL_F32) unary_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, x_stride, (float*)out, out_stride, N, act, c);
     else if (dtype == MSGL_BF16) unary_act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, N, act, c);
@@ -1137,16 +1562,28 @@ MSGL_API int msgl_unary_act(const void* x, long long x_stride, void* out, long l
 #define RT_MAX_EXPERTS 1024
 #define RT_MAX_GROUPS 64
 template <typename T>
-__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ W,
+__global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ W,
                                                     const float* __restrict__ correction, int H, int E, int n_groups, int keep,
-                                                    int top, int* __restrict__ idx, float* __restrict__ wts) {
+                                                    int top, int* __restrict__ idx, float* __restrict__ wts, int vec) {
     __shared__ float s_sh[RT_MAX_EXPERTS], c_sh[RT_MAX_EXPERTS], g_sh[RT_MAX_GROUPS];
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const T* hr = h + (size_t)t * h_stride;
     for (int e = warp; e < E; e += nw) {
         const T* wr = W + (size_t)e * H;
         float acc = 0.f;
-        for (int i = lane; i < H; i += 32) acc = fmaf(to_f32<T>(wr[i]), to_f32<T>(hr[i]), acc);
+        if (vec) {                                       // 16 bytes of the row a lane and turn
+            constexpr int V = VecOf<T>::N;
+#pragma unroll 2
+            for (int i = lane * V; i < H; i += 32 * V) {
+                float a[V], b[V];
+                VecOf<T>::load(wr + i, a);
+                VecOf<T>::load(hr + i, b);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc = fmaf(a[k], b[k], acc);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) acc = fmaf(to_f32<T>(wr[i]), to_f32<T>(hr[i]), acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) {
             const float s = sigmoidf_(acc);
@@ -1210,9 +1647,13 @@ MSGL_API int msgl_route(const void* h, long long h_stride, const void* W, const 
     if (H <= 0 || E <= 0 || E > RT_MAX_EXPERTS || n_groups < 1 || n_groups > RT_MAX_GROUPS || E % n_groups || keep < 1 || keep > n_groups ||
         top < 1 || top > keep * (E / n_groups))
         return MSGL_ERR_SIZE;
-    if (dtype == MSGL_F32) route_kernel<float><<<T_, 128, 0, stream>>>((const float*)h, h_stride, (const float*)W, correction, H, E, n_groups, keep, top, idx, wts);
-    else if (dtype == MSGL_BF16) route_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)W, correction, H, E, n_groups, keep, top, idx, wts);
-    else return MSGL_ERR_DTYPE;
+    if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
+    // whether rows can be read 16 bytes at a time: a matter of the sizes and of the weights' place, the same in every step of a model
+    const int V = dtype == MSGL_F32 ? 4 : 8;
+    const int vec = H % V == 0 && h_stride % V == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)W % 16) == 0;
+    const int threads = E > 4 ? 256 : 128;
+    if (dtype == MSGL_F32) route_kernel<float><<<T_, threads, 0, stream>>>((const float*)h, h_stride, (const float*)W, correction, H, E, n_groups, keep, top, idx, wts, vec);
+    else route_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)W, correction, H, E, n_groups, keep, top, idx, wts, vec);
     return msgl_check_launch();
 }
 

@@ -1048,6 +1048,9 @@ SIGMOID_ATTENTION_MMA_ROWS = 64     # rows of a block of the tensor-core kernel
 SIGMOID_ATTENTION_MMA_MAX_HEAD_DIM = 128
 SIGMOID_ATTENTION_SPLIT_KEYS = 256  # keys of a piece when a one-token step cuts a request's keys over several blocks
 SSM_MAX_STATE = 512
+SSM_CHUNK = 64                      # tokens of a chunk when a long portion's state-space recurrence runs in chunks side by side
+SSM_CHUNKED_FROM = 128              # the longest request's tokens from which a step runs in chunks
+SSM_CHUNK_MAX_STATE = 256           # state sizes whose chunk tiles fit shared memory
 ROUTE_MAX_EXPERTS, ROUTE_MAX_GROUPS = 1024, 64
 EXPERTS_FEW_PAIRS = 64              # up to this many (token, choice) pairs the experts' products stream the weights
 
@@ -1069,6 +1072,8 @@ def _gated_lib():
         lib.msgl_pair_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_void_p]
         lib.msgl_causal_conv_act.argtypes = [c_void_p, c_ll, c_int, c_int, c_int] + [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p]
         lib.msgl_ssm_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int] + [c_void_p] * 7 + [c_int, c_int, c_void_p]
+        lib.msgl_ssm_scan_chunked.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int] + [c_void_p] * 7 + \
+            [c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
         lib.msgl_gate_group_norm.argtypes = [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_float, c_int,
                                              c_int, c_void_p]
         lib.msgl_unary_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p]
@@ -1260,11 +1265,15 @@ def causal_conv_act(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Te
 
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, *, heads: int, groups: int, state_size: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
-             skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+             skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+             q_lens: Optional[Sequence[int]] = None, workspace=None) -> torch.Tensor:
     """State-space recurrence per head over the step's tokens, continued from and written back to `state` [slots, heads, N, P]
     float32: step = softplus(dt + dt_bias), S <- exp(-exp(a_log) step) S + step B x^T, y = S^T C + skip x, with head h on group
     h // (heads / groups).  xbc [T, heads * P + 2 groups * N] contiguous = x | B | C; dt [T, heads] a view into packed rows.
-    -> float32 [T, heads * P]."""
+    -> float32 [T, heads * P].  q_lens: the requests' numbers of tokens as the host knows them; when the longest has
+    SSM_CHUNKED_FROM or more (and the state size is at most SSM_CHUNK_MAX_STATE) the step is computed in chunks of SSM_CHUNK tokens
+    that run side by side (the same sums in float32, another order), else, and without q_lens, every request's tokens are walked in
+    order.  workspace: a parts.Workspace for the chunks' states."""
     _need_cuda(xbc, dt, dt_bias, a_log, skip, state, q_start, slots)
     T = xbc.shape[0]
     N = state_size
@@ -1275,6 +1284,18 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, *, heads: int, groups: int, st
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, N, P)
     y = torch.empty((T, heads * P), dtype=torch.float32, device=xbc.device)
     B = q_start.numel() - 1
+    if q_lens is not None and max(q_lens, default=0) >= SSM_CHUNKED_FROM and N <= SSM_CHUNK_MAX_STATE:
+        n_chunks = sum(-(-n // SSM_CHUNK) for n in q_lens)
+        numel = n_chunks * heads * (N * P + 1)
+        buf = workspace.get("ssm_chunk_states", numel, torch.float32) if workspace is not None else \
+            torch.empty(numel, dtype=torch.float32, device=xbc.device)
+        code = _gated_lib().msgl_ssm_scan_chunked(_ptr(xbc), heads, groups, N, P, _ptr(dt), _rows_view(dt, heads, "dt"), 0, _ptr(dt_bias),
+                                                  _ptr(a_log), _ptr(skip), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(y), B, n_chunks,
+                                                  _ptr(buf), _ptr(buf[n_chunks * heads * N * P:]), _dt(xbc), _stream())
+        _check(code, f"ssm_scan in chunks (state size {N})")
+        global LAUNCHES
+        LAUNCHES += 2
+        return y
     code = _gated_lib().msgl_ssm_scan(_ptr(xbc), heads, groups, N, P, _ptr(dt), _rows_view(dt, heads, "dt"), 0, _ptr(dt_bias), _ptr(a_log),
                                       _ptr(skip), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(y), B, _dt(xbc), _stream())
     _check(code, f"ssm_scan (state size {N})")

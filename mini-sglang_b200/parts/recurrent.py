@@ -129,7 +129,8 @@ class StateSpaceMixer(Mixer):
         xbc = ops.causal_conv_act(proj[:, inner:inner + cc], self.conv_w, self.conv_b, state=conv.state if self.taps > 1 else None,
                                   token_req=ctx.token_req, q_start=ctx.q_start, slots=ctx.slots)
         y = ops.ssm_scan(xbc, proj[:, inner + cc:inner + cc + self.heads], heads=self.heads, groups=self.groups, state_size=self.N,
-                         dt_bias=self.dt_bias, a_log=self.a_log, skip=self.skip, state=ssm.state, q_start=ctx.q_start, slots=ctx.slots)
+                         dt_bias=self.dt_bias, a_log=self.a_log, skip=self.skip, state=ssm.state, q_start=ctx.q_start, slots=ctx.slots,
+                         q_lens=None if ctx.uniform_decode else ctx.host_q_lens, workspace=ctx.workspace)
         act = torch.empty((x.shape[0], inner), dtype=x.dtype, device=x.device)
         ops.gate_group_norm(y, proj[:, :inner], self.norm, self.norm_groups, self.eps, act, self.out_scale)
         return ops.linear(act, self.w_out, out_dtype=torch.float32)

@@ -87,14 +87,18 @@ def row_close(row, want, dtype, bound=BF16_RMS_FRACTION_P):
     assert worst <= 6.0 * bound * scale, f"largest error {worst:.4g} is {worst / scale:.2%} of the row's rms {scale:.4g}"
 
 
+OUTLIER_RUN = 6             # positions over which a rounding outlier that entered the recurrent states may still show
+
+
 def compare(name, dtype, got, seqs, ref=None, bound=BF16_RMS_FRACTION_P):
-    """Every row against the plain implementation.  bfloat16: rounding noise has outliers (a row whose sums nearly cancel before a
-    norm), so one row in fifty (at least one) may pass the bound, none by more than two and a half times; a fault of the cache or
-    of a state moves every row behind it by more than that.  A position at which a router of the plain run chose by less than
-    CLOSE_CALL may run another expert in bfloat16 (with one expert a token that replaces the whole feed-forward output, measured
-    up to 11 % of the row's rms): such a row is held to five times the bound and counts with neither group."""
+    """Every row against the plain implementation.  float32 holds every row to 1e-4.  bfloat16: rounding noise has outliers (a row
+    whose sums nearly cancel before a norm over a few elements is normed up to unit size with its error; a router's close call
+    runs another expert), and an outlier enters the recurrent states of the layers behind it and fades over the next tokens.  So a
+    request may have one run of up to OUTLIER_RUN positions beyond the bound for every 25 of its rows (at least one), none of them
+    by more than two and a half times (five times where a router of the plain run chose by less than CLOSE_CALL).  A fault of the
+    cache or of a state moves every row behind it."""
     assert got
-    over = []
+    over = {}
     for (rid, pos), row in sorted(got.items()):
         want = ref[rid][pos] if ref is not None else plain(name, tuple(seqs[rid]))[pos]
         try:
@@ -104,13 +108,18 @@ def compare(name, dtype, got, seqs, ref=None, bound=BF16_RMS_FRACTION_P):
                 close = ref is None and close_call(name, tuple(seqs[rid]), pos)
                 try:
                     row_close(row, want, dtype, (5.0 if close else 2.5) * bound)
-                    if not close:
-                        over.append((rid, pos))
+                    over.setdefault(rid, []).append(pos)
                     continue
                 except AssertionError:
                     pass
             raise AssertionError(f"request {rid!r} position {pos} ({dtype}, {name}): {e}") from None
-    assert len(over) <= max(1, len(got) // 50), f"{len(over)} of {len(got)} rows beyond the bound ({dtype}, {name}): {over[:8]}"
+    for rid, places in over.items():
+        runs, start = 0, None
+        for pos in places:
+            if start is None or pos >= start + OUTLIER_RUN:
+                runs, start = runs + 1, pos
+        rows = sum(1 for k in got if k[0] == rid)
+        assert runs <= max(1, rows // 25), f"request {rid!r}: {runs} runs of rows beyond the bound among {rows} ({dtype}, {name}): {places}"
 
 
 def poison(r):
@@ -167,6 +176,10 @@ def test_activations_and_gated_group_norm(dtype):
     packed = torch.cat((torch.zeros(5, 3, dtype=dt), x, torch.zeros(5, 2, dtype=dt)), dim=1).cuda()
     got = ops.unary_act(packed[:, 3:80], ops.ACT_RELU2, 0.7).float().cpu()
     torch.testing.assert_close(got, (torch.relu(x.float()) ** 2 * 0.7).to(dt).float(), **tol_of(dtype, 1e-6, 1e-2))
+    wide = (3 * torch.randn(6, 96, generator=g)).to(dt).cuda()                      # rows that 16-byte reads can take
+    for act, f in ((ops.ACT_RELU2, lambda v: torch.relu(v) ** 2), (ops.ACT_SILU, pp.silu)):
+        got = ops.unary_act(wide[:, 8:88], act, 0.7).float().cpu()
+        torch.testing.assert_close(got, (f(wide[:, 8:88].float().cpu()) * 0.7).to(dt).float(), **tol_of(dtype, 1e-6, 1e-2))
     for N, parts in ((96, 2), (40, 1), (48, 6), (192, 4), (520, 5)):
         y = 2 * torch.randn(7, N, generator=g)
         z = torch.randn(7, N + 9, generator=g).to(dt)
@@ -429,20 +442,26 @@ def test_min_gru_in_portions_and_batches(dtype, W, long):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("geo", [dict(heads=4, P=12, N=16, groups=2, K=3), dict(heads=1, P=20, N=8, groups=1, K=1),
                                  dict(heads=6, P=8, N=40, groups=3, K=2), dict(heads=2, P=40, N=24, groups=1, K=4),
-                                 dict(heads=8, P=64, N=128, groups=8, K=4)])
-def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo):
+                                 dict(heads=8, P=64, N=128, groups=8, K=4, lead=8), dict(heads=2, P=72, N=136, groups=2, K=2),
+                                 dict(heads=8, P=16, N=16, groups=2, K=3, lead=16)])
+@pytest.mark.parametrize("long", [False, True])
+def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo, long):
     """The short convolution continued from a request's last inputs (portions shorter than the taps among them) and the scan
-    continued from its state, three requests in shared steps, against the recurrence written out; steps from tiny to large."""
+    continued from its state, three requests in shared steps, against the recurrence written out; steps from tiny to large.
+    long: portions that run in chunks side by side (whole chunks, a last chunk of one token, single tokens of one request beside a
+    long portion of another, single tokens after a step in chunks)."""
     from mini_sglang_b200 import ops
     heads, P, N, groups, K = geo["heads"], geo["P"], geo["N"], geo["groups"], geo["K"]
+    lead = geo.get("lead", 3)             # columns before the convolution's in the packed rows: 3 = rows that no 16-byte read can take
     g = torch.Generator().manual_seed(N + K)
     dt = DT[dtype]
     inner, gn = heads * P, groups * N
     C = inner + 2 * gn
-    lens = {0: 70, 1: 37, 2: 64}
-    u = {r: torch.randn(n, 3 + C + heads, generator=g).to(dt) for r, n in lens.items()}
+    lens = {0: 330, 1: 137, 2: 200} if long else {0: 70, 1: 37, 2: 64}
+    cuts = {0: [1] * 60 + [270], 1: [130, 2, 2, 3], 2: [5, 129, 1, 1, 64]} if long else {0: [1] * 70, 1: [30, 2, 2, 3], 2: [1, 1, 2, 43, 1, 16]}
+    u = {r: torch.randn(n, lead + C + heads, generator=g).to(dt) for r, n in lens.items()}
     for r in u:
-        u[r][:, 3 + C:] *= 3.0                          # step inputs: softplus from nearly 0 to several
+        u[r][:, lead + C:] *= 3.0                          # step inputs: softplus from nearly 0 to several
     taps, cb = 0.5 * torch.randn(C, K, generator=g), 0.1 * torch.randn(C, generator=g)
     dtb, alog, skip = 0.5 * torch.randn(heads, generator=g), 0.5 * torch.randn(heads, generator=g), 1 + 0.1 * torch.randn(heads, generator=g)
     conv_state = torch.full((5, max(K - 1, 0), C), float("nan"), dtype=dt).cuda()
@@ -456,17 +475,17 @@ def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo):
         q_start = i32(np.concatenate(([0], np.cumsum(ns))).tolist())
         slots = i32([r + 1 for r in reqs])
         token_req = i32([i for i, n in enumerate(ns) for _ in range(n)])
-        xbc = ops.causal_conv_act(x[:, 3:3 + C], tw, cb.cuda(), state=conv_state if K > 1 else None, token_req=token_req,
+        xbc = ops.causal_conv_act(x[:, lead:lead + C], tw, cb.cuda(), state=conv_state if K > 1 else None, token_req=token_req,
                                   q_start=q_start, slots=slots)
-        return ops.ssm_scan(xbc, x[:, 3 + C:], heads=heads, groups=groups, state_size=N, dt_bias=dtb.cuda(), a_log=alog.cuda(),
-                            skip=skip.cuda(), state=ssm_state, q_start=q_start, slots=slots)
+        return ops.ssm_scan(xbc, x[:, lead + C:], heads=heads, groups=groups, state_size=N, dt_bias=dtb.cuda(), a_log=alog.cuda(),
+                            skip=skip.cuda(), state=ssm_state, q_start=q_start, slots=slots, q_lens=list(ns) if long else None)
 
     def want(x):
         f = x.double()
         n = f.shape[0]
-        xbc = pp.silu(pp.causal_conv(f[:, 3:3 + C], taps.double(), cb.double())).to(dt).double()      # the scan reads rounded rows
+        xbc = pp.silu(pp.causal_conv(f[:, lead:lead + C], taps.double(), cb.double())).to(dt).double()      # the scan reads rounded rows
         xs, B, Cc = xbc[:, :inner].view(n, heads, P), xbc[:, inner:inner + gn].view(n, groups, N), xbc[:, inner + gn:].view(n, groups, N)
-        step = torch.nn.functional.softplus(f[:, 3 + C:] + dtb, threshold=1e9)
+        step = torch.nn.functional.softplus(f[:, lead + C:] + dtb, threshold=1e9)
         S, rows = torch.zeros(heads, N, P, dtype=F64), []
         for t in range(n):
             y = torch.zeros(heads, P, dtype=F64)
@@ -477,12 +496,12 @@ def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo):
             rows.append(y.reshape(-1))
         return torch.stack(rows).float()
 
-    got = _shared_steps(lens, {0: [1] * 70, 1: [30, 2, 2, 3], 2: [1, 1, 2, 43, 1, 16]}, (2, 0, 1), run)
-    for r in lens:
-        torch.testing.assert_close(got[r], want(u[r]), **tol_of(dtype, 5e-5, 3e-2))
+    got = _shared_steps(lens, cuts, (2, 0, 1), run)
+    for r in lens:                       # in chunks the sums of up to N + 64 terms of size 1 to 10 come in another order
+        torch.testing.assert_close(got[r], want(u[r]), **tol_of(dtype, 2e-4 if long else 5e-5, 3e-2))
     conv_state[1].zero_()
     ssm_state[1].zero_()                                   # request 0's rows, handed to a new request
-    u[0] = torch.randn(9, 3 + C + heads, generator=g).to(dt)
+    u[0] = torch.randn(9, lead + C + heads, generator=g).to(dt)
     got = _shared_steps({0: 9}, {0: [2, 1, 6]}, (0,), run)
     torch.testing.assert_close(got[0], want(u[0]), **tol_of(dtype, 5e-5, 3e-2))
 
@@ -492,10 +511,11 @@ def test_convolution_and_state_space_scan_in_portions_and_batches(dtype, geo):
 # ---------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("geo", [dict(E=8, count=4, keep=2, top=3), dict(E=5, count=5, keep=2, top=1), dict(E=6, count=1, keep=1, top=2),
-                                 dict(E=16, count=4, keep=2, top=4), dict(E=64, count=8, keep=3, top=6), dict(E=12, count=2, keep=1, top=6)])
+                                 dict(E=16, count=4, keep=2, top=4), dict(E=64, count=8, keep=3, top=6), dict(E=12, count=2, keep=1, top=6),
+                                 dict(E=8, count=4, keep=2, top=3, H=37), dict(E=16, count=4, keep=2, top=4, H=600)])
 def test_router_choice_and_weights(dtype, geo):
     from mini_sglang_b200 import ops
-    E, H, T = geo["E"], 40, 50
+    E, H, T = geo["E"], geo.get("H", 40), 50
     g = torch.Generator().manual_seed(E)
     dt = DT[dtype]
     h = torch.randn(T, H, generator=g).to(dt)
@@ -593,6 +613,33 @@ def test_whole_prompt_token_by_token_and_in_portions(name, dtype):
     compare(name, dtype, got, seqs)
     assert len(got) == n
     r.mgr.check_idle()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["PA", "PB", "PC"])
+def test_long_prompt_whole_and_in_long_and_short_portions(name, dtype):
+    """A prompt long enough for the recurrences to run in chunks side by side and for the attention to take several tiles of queries:
+    in one step; and in portions of which some run in chunks and some token by token, with a second request's single tokens beside
+    them.  Every position of both against the plain implementation."""
+    V = CONFIGS_P[name]["vocab"]
+    n = 261
+    toks, other = random_tokens(n, V, 900 + n), random_tokens(9, V, 77)
+    seqs = {"w": toks, "p": toks, "o": other}
+    r = runner(name, dtype, num_pages=2 * (-(-n // PAGE[name])) + 24)
+    poison(r)
+    got = play(r, [{"entries": [("w", toks, list(range(n)))], "end": ["w"]}])
+    compare(name, dtype, got, seqs)
+    sizes, at, steps = [150, 1, 64, 2, 44], 0, []
+    for i, c in enumerate(sizes):
+        entries = [("p", toks[at:at + c], list(range(c)))]
+        if i < len(other):
+            entries.insert(i % 2, ("o", other[i:i + 1], [0]))
+        steps.append({"entries": entries})
+        at += c
+    assert at == n
+    got = play(r, steps)
+    compare(name, dtype, got, seqs)
+    assert len(got) == n + len(sizes)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
