@@ -906,15 +906,15 @@ __global__ void causal_conv_act_kernel(const void* in_, long long stride, int of
     reinterpret_cast<T*>(out_)[(size_t)t * C + c] = from_f32<T>(acc);
 }
 
-// The same with 16 bytes of channels a thread and CV_TB tokens in turn, for up to 4 taps: the request's last three inputs stay in
-// registers from token to token.  A tap that does not exist (fewer than 4) has weight 0 and is not read; the sum of a token is the
+// The same with 16 bytes of channels a thread and `tb` tokens in turn (CV_TB in a long step, 1 in a short one, where the tokens
+// are better walked side by side), for up to 4 taps: the request's last three inputs stay in registers from token to token.  A tap that does not exist (fewer than 4) has weight 0 and is not read; the sum of a token is the
 // same sequence of multiply-adds as above.
 #define CV_TB 8
 template <typename T>
 __global__ void __launch_bounds__(128)
 causal_conv_act_vec_kernel(const void* in_, long long stride, int off, int C, int K, const float* __restrict__ w, const float* __restrict__ bias,
                            const void* state_, const int* __restrict__ token_req, const int* __restrict__ q_start,
-                           const int* __restrict__ slots, void* out_, int act, int T_) {
+                           const int* __restrict__ slots, void* out_, int act, int T_, int tb) {
     constexpr int V = VecOf<T>::N;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (c >= C) return;
@@ -930,8 +930,8 @@ causal_conv_act_vec_kernel(const void* in_, long long stride, int off, int C, in
 #pragma unroll
     for (int i = 0; i < V; ++i) bv[i] = bias ? bias[c + i] : 0.f;
     int prev = -1;
-    for (int tt = 0; tt < CV_TB; ++tt) {
-        const int t = blockIdx.y * CV_TB + tt;
+    for (int tt = 0; tt < tb; ++tt) {
+        const int t = blockIdx.y * tb + tt;
         if (t >= T_) break;
         const int r = token_req[t];
         if (r != prev) {                                 // the window of the request's inputs before t
@@ -993,9 +993,10 @@ MSGL_API int msgl_causal_conv_act(const void* in, long long stride, int off, int
     const bool vec = K <= 4 && C % V == 0 && stride % V == 0 && off % V == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
                      ((uintptr_t)state % 16) == 0 && (stride * (long long)item) % 16 == 0;
     if (vec) {
-        const dim3 grid((C / V + threads - 1) / threads, (T_ + CV_TB - 1) / CV_TB);
-        if (dtype == MSGL_F32) causal_conv_act_vec_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_);
-        else causal_conv_act_vec_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_);
+        const int tb = T_ >= 64 * CV_TB ? CV_TB : 1;
+        const dim3 grid((C / V + threads - 1) / threads, (T_ + tb - 1) / tb);
+        if (dtype == MSGL_F32) causal_conv_act_vec_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_, tb);
+        else causal_conv_act_vec_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act, T_, tb);
     } else {
         const dim3 grid((C + threads - 1) / threads, T_);
         if (dtype == MSGL_F32) causal_conv_act_kernel<float><<<grid, threads, 0, stream>>>(in, stride, off, C, K, w, bias, state, token_req, q_start, slots, out, act);
@@ -1292,13 +1293,21 @@ __global__ void ssm_chunk_carry_kernel(int heads, int NPel, const int* __restric
     float S = *Sg;
     const size_t step = (size_t)heads * NPel;
     size_t idx = ((size_t)first * heads + h) * NPel + e;
-    float own = U[idx];
-    for (int c = 0; c < nc; ++c) {
-        const float next = c + 1 < nc ? U[idx + step] : 0.f;
-        U[idx] = S;
-        S = fmaf(Adec[(size_t)(first + c) * heads + h], S, own);
-        own = next;
-        idx += step;
+    for (int c0 = 0; c0 < nc; c0 += 8) {                 // eight chunks' reads in flight, then their updates in order
+        float own[8], dec[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c0 + i < nc) {
+                own[i] = U[idx + i * step];
+                dec[i] = Adec[(size_t)(first + c0 + i) * heads + h];
+            }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c0 + i < nc) {
+                U[idx + i * step] = S;
+                S = fmaf(dec[i], S, own[i]);
+            }
+        idx += 8 * step;
     }
     *Sg = S;
 }
@@ -1383,22 +1392,29 @@ ssm_chunk_out_kernel(const void* xbc_, int heads, int groups, int N, int P, cons
             acc[a][3] = fmaf(w, xv.w, acc[a][3]);
         }
     }
-    const float* S = U + (((size_t)(first + ci) * heads + h) * N) * P;     // the state at the chunk's start
-    const int pc = p0 + tp * 4;
+    // the state at the chunk's start goes through the shared memory that held B (N * SC_PT <= SC_L * NS floats)
+    const float* S = U + (((size_t)(first + ci) * heads + h) * N) * P;
+    float* Ss = Bs;                          // [N][SC_PT], zero beyond the head's columns
     const bool vec = (P & 3) == 0;
+    if (vec) {
+        for (int e = tid; e < N * (SC_PT / 4); e += SC_THREADS) {
+            const int k = e / (SC_PT / 4), q = (e - k * (SC_PT / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p0 + q < P) v = *reinterpret_cast<const float4*>(S + (size_t)k * P + p0 + q);
+            *reinterpret_cast<float4*>(Ss + k * SC_PT + q) = v;
+        }
+    } else {
+        for (int e = tid; e < N * SC_PT; e += SC_THREADS) {
+            const int k = e / SC_PT, q = e - k * SC_PT;
+            Ss[e] = p0 + q < P ? S[(size_t)k * P + p0 + q] : 0.f;
+        }
+    }
+    __syncthreads();
+    const int pc = p0 + tp * 4;
     if (pc < P) {
 #pragma unroll 4
         for (int k = 0; k < N; ++k) {
-            float4 sv;
-            if (vec) {
-                sv = *reinterpret_cast<const float4*>(S + (size_t)k * P + pc);
-            } else {
-                const float* sp = S + (size_t)k * P + pc;
-                sv.x = sp[0];
-                sv.y = pc + 1 < P ? sp[1] : 0.f;
-                sv.z = pc + 2 < P ? sp[2] : 0.f;
-                sv.w = pc + 3 < P ? sp[3] : 0.f;
-            }
+            const float4 sv = *reinterpret_cast<const float4*>(Ss + k * SC_PT + tp * 4);
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
                 const float c = Cs[(ti + 16 * a) * NS + k];
