@@ -177,8 +177,8 @@ def parse_lengths(spec, batch):
     return out
 
 
-def profile_kernels(step, n_steps, captures=lambda: 0):
-    """-> {kernel name: [launches a step, mean microseconds]} of the twelve kernels that `n_steps` calls of step() spend the
+def profile_kernels(step, n_steps, captures=lambda: 0, most=12):
+    """-> {kernel name: [launches a step, mean microseconds]} of the `most` kernels that `n_steps` calls of step() spend the
     most time in, from the CUDA profiler's trace (kernels inside a replayed graph included).  `captures()` counts the CUDA
     graphs made so far: a trace during which one was captured (its warm-up runs are in it) is taken again."""
     import torch
@@ -198,7 +198,7 @@ def profile_kernels(step, n_steps, captures=lambda: 0):
             a = acc.setdefault(name, [0, 0.0])
             a[0] += 1
             a[1] += e.time_range.end - e.time_range.start
-    top = sorted(acc.items(), key=lambda kv: -kv[1][1])[:12]
+    top = sorted(acc.items(), key=lambda kv: -kv[1][1])[:most]
     return {k: [round(v[0] / n_steps, 1), round(v[1] / v[0], 1)] for k, v in top}
 
 
@@ -656,7 +656,7 @@ def workload_vekurax(args, name="vekurax", config=None, beside="qwen3"):
             e1.record()
             torch.cuda.synchronize()
             pre_ms = e0.elapsed_time(e1) / 5
-            pre_kernels = profile_kernels(prefill_step, 2)
+            pre_kernels = profile_kernels(prefill_step, 2, most=24)
             slots = [runner.open() for _ in range(B)]
             for slot in slots:
                 ctx_toks = rand(CTX - (W + K) - 8)
@@ -676,7 +676,7 @@ def workload_vekurax(args, name="vekurax", config=None, beside="qwen3"):
             e1.record()
             torch.cuda.synchronize()
             dec_ms = e0.elapsed_time(e1) / K
-            dec_kernels = profile_kernels(decode_step, 3, captures=lambda: len(runner._graphs))
+            dec_kernels = profile_kernels(decode_step, 3, captures=lambda: len(runner._graphs), most=24)
             res[arch] = {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PREFILL / pre_ms * 1e3, 1),
                          "decode_ms_per_step": round(dec_ms, 4), "decode_tok_s": round(B / dec_ms * 1e3, 1),
                          "decode_graph": bool(runner.last_step_used_graph), "prefill_kernels": pre_kernels, "decode_kernels": dec_kernels}
