@@ -20,9 +20,11 @@ class RoutedExperts(FeedForward):
     the weighted sum of the chosen experts' outputs, in float32, times `out_scale`.
 
     A few (token, choice) pairs - and every step that a CUDA graph replays - read the chosen experts' rows straight from the
-    stacked weights (two launches whatever the choice).  Many tokens are put in the order of their experts on the device; the
-    host reads the experts' counts (one small copy) and runs one gate/up product with its activation and one down product per
-    expert that has tokens, on the engine's matrix products; one kernel sums every token's rows with their weights.
+    stacked weights (two launches whatever the choice).  Many tokens are put in the order of their experts on the device; in
+    bfloat16 the library's grouped matrix product then runs every expert's gate/up rows in one launch and every down product in
+    another, with the experts' row ranges read on the device (rows of bfloat16, summed in float32); in float32, or where the
+    sizes are no multiples of 8, the host reads the experts' counts (one small copy) and runs one gate/up product with its
+    activation and one down product per expert that has tokens.  One kernel sums every token's rows with their weights.
 
     params: hidden_size, intermediate_size, num_experts, top, groups, keep_groups, out_scale,
             names (router, correction, expert (with {e} for the expert's number), gate, up, down).
@@ -74,6 +76,12 @@ class RoutedExperts(FeedForward):
             return ops.experts_few(x, self.gate_up, self.down, idx, wts, self.out_scale)
         counts, place = ops.expert_order(idx, self.n_exp)
         rows = ops.expert_gather(x, place, self.top)
+        if x.dtype == torch.bfloat16 and self.H % 8 == 0 and self.F % 8 == 0 and hasattr(torch, "_grouped_mm"):
+            # the library's grouped product takes the experts' row ranges from the device: two launches, nothing read on the host
+            ends = torch.cumsum(counts, 0, dtype=torch.int32)
+            a = ops.swiglu(torch._grouped_mm(rows, self.gate_up.view(self.n_exp, 2 * self.F, self.H).transpose(-2, -1), offs=ends))
+            y = torch._grouped_mm(a, self.down.transpose(-2, -1), offs=ends)
+            return ops.expert_combine(y, place, wts, self.out_scale)
         y = torch.empty((T * self.top, self.H), dtype=torch.float32, device=x.device)
         at = 0
         for e, n in enumerate(counts.tolist()):          # the one read of device data on the host: the experts' row counts
