@@ -707,7 +707,7 @@ def main():
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
     ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare", "pepevik_compare"],
-                    help="headline: the line the contract names; the others: further workloads, one JSON line each")
+                    help="headline: the default line; the others: further workloads, one JSON line each")
     ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare / pepevik_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")

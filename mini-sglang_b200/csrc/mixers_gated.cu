@@ -1499,9 +1499,11 @@ __global__ void gate_group_norm_kernel(const float* __restrict__ y, int N, int p
     const T* zr = reinterpret_cast<const T*>(z_) + (size_t)t * z_stride + (size_t)g * n;
     T* orow = reinterpret_cast<T*>(out_) + (size_t)t * out_stride + (size_t)g * n;
     float ss = 0.f;
+#pragma unroll 8
     for (int i = lane; i < n; i += 32) { const float v = yr[i] * siluf_(to_f32<T>(zr[i])); ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     const float f = rsqrtf(ss / (float)n + eps) * c;
+#pragma unroll 8
     for (int i = lane; i < n; i += 32)
         orow[i] = from_f32<T>(yr[i] * siluf_(to_f32<T>(zr[i])) * f * w[(size_t)g * n + i]);
 }
