@@ -6,11 +6,16 @@
 //                              (of head sizes of their own) into the paged cache
 //   sigmoid_attention_kernel   causal attention whose weight of a key is sigmoid(q.k * scale + bias[head][distance]): no sum
 //                              over keys divides anything, so pieces of the keys simply add up (sum_pieces_kernel)
+//   sigmoid_attention_mma_kernel   the same for bfloat16 with both products on mma.sync tiles (64 rows a block, float32 scores)
 //   mingru_kernel              S_t = (1 - z_t) S_(t-1) + z_t c_t per channel with gates from the current token, times silu(g)
+//   mingru_chunk_sum_kernel, mingru_chunk_out_kernel      long portions: chunks of the tokens side by side
 //   pair_norm_kernel           c * (rms(a) * wa + rms(b) * wb) in float32: two mixers' outputs joined
-//   causal_conv_act_kernel     short causal convolution per channel with bias and silu, continued from a request's last inputs;
+//   causal_conv_act_kernel     short causal convolution per channel with bias and silu, continued from a request's last inputs
+//                              (causal_conv_act_vec_kernel: 16 bytes of channels a thread where the rows allow it);
 //                              conv_state_shift_kernel brings those up to date
 //   ssm_scan_kernel            S_t = exp(-exp(A) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t per head, token by token
+//   ssm_chunk_state_kernel, ssm_chunk_carry_kernel, ssm_chunk_out_kernel     long portions: chunks of 64 tokens side by side
+//                              (a chunk's own sum and decay; the chunks' start states in order; outputs from both)
 //   gate_group_norm_kernel     (y * silu(z)) RMS-normed in equal parts of the row, times a weight
 //   unary_act_kernel           relu(x)^2 (and the other activations), times a constant
 //   route_kernel               router logits in float32, sigmoid scores, correction, limitation to the best groups, the top
