@@ -137,6 +137,7 @@ COMMON_SOURCES = ["elementwise.cu", "sampling.cu", "gemm_small_m.cu", "gemm_tc.c
 ATTENTION_SOURCES = ["attention.cu"]
 MIXER_SOURCES = ["mixers.cu"]
 GATED_MIXER_SOURCES = ["mixers_gated.cu"]
+DELTA_MIXER_SOURCES = ["mixers_delta.cu"]
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))   # head sizes the tensor-core attention kernel is built for
 
 
@@ -158,6 +159,12 @@ def gated_mixers_library() -> ctypes.CDLL:
     """The kernels of csrc/mixers_gated.cu (sigmoid attention, gated recurrences, state-space scan, routed experts); built
     only for models that have such parts."""
     return load_library("mixers_gated", GATED_MIXER_SOURCES)
+
+
+def delta_mixers_library() -> ctypes.CDLL:
+    """The kernels of csrc/mixers_delta.cu (attention with a sink, the gated delta rule, scaled sums, the per-layer token
+    input); built only for models that have such parts."""
+    return load_library("mixers_delta", DELTA_MIXER_SOURCES)
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
@@ -190,7 +197,7 @@ def decode_step_library(head_dim: int) -> ctypes.CDLL:
 def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
     """Compile every library ahead of time (used by the repository's build check)."""
     paths = [compile_library("common", COMMON_SOURCES), compile_library("mixers", MIXER_SOURCES),
-             compile_library("mixers_gated", GATED_MIXER_SOURCES)]
+             compile_library("mixers_gated", GATED_MIXER_SOURCES), compile_library("mixers_delta", DELTA_MIXER_SOURCES)]
     for hd in head_dims:
         paths.append(compile_library(f"attention_d{hd}", ATTENTION_SOURCES, {"MSGL_HEAD_DIM": hd}))
     paths.append(compile_library("attention_noalloc_d128", ["attention_noalloc.cu"], {"MSGL_HEAD_DIM": 128}))

@@ -20,8 +20,12 @@
 //   unary_act_kernel           relu(x)^2 (and the other activations), times a constant
 //   route_kernel               router logits in float32, sigmoid scores, correction, limitation to the best groups, the top
 //                              experts and their weights: one block per token
+//                              (or, in its softmax mode, the largest logits and the softmax over the chosen ones; a further row's
+//                              sigmoid per token beside them)
 //   expert_gate_up_kernel, expert_down_kernel      the chosen experts' products for a few tokens, straight from the experts'
-//                              stacked weights (weight-streaming, one warp per output row)
+//                              stacked weights (weight-streaming, one warp per output row); silu(gate) * up or the clamped
+//                              form; an extra term (a shared expert's output times a gate per token) joins the sum
+//   clamped_glu_kernel         min(gate, limit) * sigmoid(1.702 ...) * (clamp(up) + 1) of a packed [gate | up] row
 //   expert_count_kernel, expert_place_kernel, expert_gather_kernel, expert_combine_kernel    many tokens: the (token, choice)
 //                              pairs in the order of their experts (stable), rows gathered for one product per expert, and the
 //                              weighted sum of every token's rows
@@ -38,6 +42,11 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float gelu_tanhf_(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// a gated activation with bounded inputs: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float clamped_gluf_(float gate, float up, float limit) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g * sigmoidf_(1.702f * g) * (u + 1.f);
 }
 // ln(1 + e^x) without a threshold: max(x, 0) + ln(1 + e^-|x|)
 __device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
@@ -1587,12 +1596,14 @@ MSGL_API int msgl_unary_act(const void* x, long long x_stride, void* out, long l
 template <typename T>
 __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ W,
                                                     const float* __restrict__ correction, int H, int E, int n_groups, int keep,
-                                                    int top, int* __restrict__ idx, float* __restrict__ wts, int vec) {
+                                                    int top, int* __restrict__ idx, float* __restrict__ wts, int vec, int softmax,
+                                                    const T* __restrict__ gate_row, float* __restrict__ gate_out) {
     __shared__ float s_sh[RT_MAX_EXPERTS], c_sh[RT_MAX_EXPERTS], g_sh[RT_MAX_GROUPS];
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const T* hr = h + (size_t)t * h_stride;
-    for (int e = warp; e < E; e += nw) {
-        const T* wr = W + (size_t)e * H;
+    // row E, if there is one, is no expert: the sigmoid of its product with the token is handed out beside the choice
+    for (int e = warp; e < E + (gate_row ? 1 : 0); e += nw) {
+        const T* wr = e < E ? W + (size_t)e * H : gate_row;
         float acc = 0.f;
         if (vec) {                                       // 16 bytes of the row a lane and turn
             constexpr int V = VecOf<T>::N;
@@ -1609,9 +1620,16 @@ __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ h, lon
         }
         acc = warp_sum(acc);
         if (lane == 0) {
-            const float s = sigmoidf_(acc);
-            s_sh[e] = s;
-            c_sh[e] = s + (correction ? correction[e] : 0.f);
+            if (e >= E) {
+                gate_out[t] = sigmoidf_(acc);
+            } else if (softmax) {                        // the logits themselves are chosen by and weighted
+                s_sh[e] = acc;
+                c_sh[e] = acc;
+            } else {
+                const float s = sigmoidf_(acc);
+                s_sh[e] = s;
+                c_sh[e] = s + (correction ? correction[e] : 0.f);
+            }
         }
     }
     __syncthreads();
@@ -1641,7 +1659,7 @@ __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ h, lon
         __syncthreads();
     }
     if (warp == 0) {
-        float total = 0.f;
+        float total = 0.f, first = 0.f;
         for (int k = 0; k < top; ++k) {
             float bv = -INFINITY; int be = 0x7fffffff;
             for (int e = lane; e < E; e += 32) {
@@ -1656,16 +1674,23 @@ __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ h, lon
             }
             if (be >= E) be = 0;                          // nothing left to choose from (top > experts allowed): refused on the host
             if (lane == 0) { idx[(size_t)t * top + k] = be; c_sh[be] = NAN; }
-            total += s_sh[be];
+            if (k == 0) first = s_sh[be];                 // the largest chosen logit: the softmax's reference
+            total += softmax ? expf(s_sh[be] - first) : s_sh[be];
             __syncwarp();
         }
-        const float inv = 1.f / (total + 1e-20f);
-        for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = s_sh[idx[(size_t)t * top + k]] * inv;
+        if (softmax) {                                    // softmax over the chosen logits only
+            const float inv = 1.f / total;
+            for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = expf(s_sh[idx[(size_t)t * top + k]] - first) * inv;
+        } else {
+            const float inv = 1.f / (total + 1e-20f);
+            for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] = s_sh[idx[(size_t)t * top + k]] * inv;
+        }
     }
 }
 
 MSGL_API int msgl_route(const void* h, long long h_stride, const void* W, const float* correction, int H, int E, int n_groups, int keep,
-                        int top, int* idx, float* wts, int T_, int dtype, cudaStream_t stream) {
+                        int top, int* idx, float* wts, int T_, int dtype, int softmax, const void* gate_row, float* gate_out,
+                        cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
     if (H <= 0 || E <= 0 || E > RT_MAX_EXPERTS || n_groups < 1 || n_groups > RT_MAX_GROUPS || E % n_groups || keep < 1 || keep > n_groups ||
         top < 1 || top > keep * (E / n_groups))
@@ -1673,10 +1698,12 @@ MSGL_API int msgl_route(const void* h, long long h_stride, const void* W, const 
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     // whether rows can be read 16 bytes at a time: a matter of the sizes and of the weights' place, the same in every step of a model
     const int V = dtype == MSGL_F32 ? 4 : 8;
-    const int vec = H % V == 0 && h_stride % V == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)W % 16) == 0;
+    const int vec = H % V == 0 && h_stride % V == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)W % 16) == 0 &&
+                    ((uintptr_t)gate_row % 16) == 0;
+    if (gate_row && !gate_out) return MSGL_ERR_SIZE;
     const int threads = E > 4 ? 256 : 128;
-    if (dtype == MSGL_F32) route_kernel<float><<<T_, threads, 0, stream>>>((const float*)h, h_stride, (const float*)W, correction, H, E, n_groups, keep, top, idx, wts, vec);
-    else route_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)W, correction, H, E, n_groups, keep, top, idx, wts, vec);
+    if (dtype == MSGL_F32) route_kernel<float><<<T_, threads, 0, stream>>>((const float*)h, h_stride, (const float*)W, correction, H, E, n_groups, keep, top, idx, wts, vec, softmax, (const float*)gate_row, gate_out);
+    else route_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)W, correction, H, E, n_groups, keep, top, idx, wts, vec, softmax, (const __nv_bfloat16*)gate_row, gate_out);
     return msgl_check_launch();
 }
 
@@ -1689,7 +1716,8 @@ MSGL_API int msgl_route(const void* h, long long h_stride, const void* W, const 
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) expert_gate_up_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ Wgu,
-                                                             const int* __restrict__ idx, int top, int H, int F, T* __restrict__ act) {
+                                                             const int* __restrict__ idx, int top, int H, int F, T* __restrict__ act,
+                                                             float limit) {
     const int pair = blockIdx.y, t = pair / top;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= F) return;
@@ -1704,13 +1732,14 @@ __global__ void __launch_bounds__(256) expert_gate_up_kernel(const T* __restrict
         au = fmaf(to_f32<T>(u[i]), x, au);
     }
     ag = warp_sum(ag); au = warp_sum(au);
-    if (lane == 0) act[(size_t)pair * F + r] = from_f32<T>(siluf_(ag) * au);
+    if (lane == 0) act[(size_t)pair * F + r] = from_f32<T>(limit > 0.f ? clamped_gluf_(ag, au, limit) : siluf_(ag) * au);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) expert_down_kernel(const T* __restrict__ act, const T* __restrict__ Wd, const int* __restrict__ idx,
                                                           const float* __restrict__ wts, int top, int H, int F, float c_out,
-                                                          float* __restrict__ out) {
+                                                          float* __restrict__ out, const float* __restrict__ extra,
+                                                          const float* __restrict__ extra_gate) {
     const int t = blockIdx.y;
     const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (c >= H) return;
@@ -1724,23 +1753,26 @@ __global__ void __launch_bounds__(256) expert_down_kernel(const T* __restrict__ 
         acc = warp_sum(acc);
         total = fmaf(wts[(size_t)t * top + k], acc, total);
     }
-    if (lane == 0) out[(size_t)t * H + c] = total * c_out;
+    if (lane == 0) {
+        if (extra) total = fmaf(extra_gate ? extra_gate[t] : 1.f, extra[(size_t)t * H + c], total);
+        out[(size_t)t * H + c] = total * c_out;
+    }
 }
 
 MSGL_API int msgl_experts_few(const void* h, long long h_stride, const void* Wgu, const void* Wd, const int* idx,
                               const float* wts, int top, int H, int F, void* act, float c_out, float* out, int T_, int dtype,
-                              cudaStream_t stream) {
+                              float limit, const float* extra, const float* extra_gate, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
     if (top < 1 || H <= 0 || F <= 0) return MSGL_ERR_SIZE;
     if (dtype != MSGL_F32 && dtype != MSGL_BF16) return MSGL_ERR_DTYPE;
     const dim3 g1((F + 7) / 8, T_ * top), g2((H + 7) / 8, T_);
     if (dtype == MSGL_F32) {
-        expert_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, h_stride, (const float*)Wgu, idx, top, H, F, (float*)act);
-        expert_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)act, (const float*)Wd, idx, wts, top, H, F, c_out, out);
+        expert_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, h_stride, (const float*)Wgu, idx, top, H, F, (float*)act, limit);
+        expert_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)act, (const float*)Wd, idx, wts, top, H, F, c_out, out, extra, extra_gate);
     } else {
         expert_gate_up_kernel<__nv_bfloat16><<<g1, 256, 0, stream>>>((const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)Wgu, idx, top, H, F,
-                                                                      (__nv_bfloat16*)act);
-        expert_down_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)Wd, idx, wts, top, H, F, c_out, out);
+                                                                      (__nv_bfloat16*)act, limit);
+        expert_down_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)Wd, idx, wts, top, H, F, c_out, out, extra, extra_gate);
     }
     return msgl_check_launch();
 }
@@ -1799,11 +1831,14 @@ __global__ void expert_gather_kernel(const T* __restrict__ h, long long h_stride
 
 template <typename Y>
 __global__ void expert_combine_kernel(const Y* __restrict__ y, const int* __restrict__ place, const float* __restrict__ wts, int top, int H,
-                                      float c, float* __restrict__ out) {
+                                      float c, float* __restrict__ out, const float* __restrict__ extra,
+                                      const float* __restrict__ extra_gate) {
     const int t = blockIdx.x;
+    const float eg = extra ? (extra_gate ? extra_gate[t] : 1.f) : 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) acc = fmaf(wts[(size_t)t * top + k], to_f32<Y>(y[(size_t)place[(size_t)t * top + k] * H + i]), acc);
+        if (extra) acc = fmaf(eg, extra[(size_t)t * H + i], acc);
         out[(size_t)t * H + i] = acc * c;
     }
 }
@@ -1826,9 +1861,35 @@ MSGL_API int msgl_expert_gather(const void* h, long long h_stride, const int* pl
 }
 
 MSGL_API int msgl_expert_combine(const void* y, int y_is_f32, const int* place, const float* wts, int top, int H, float c, float* out,
-                                 int T_, cudaStream_t stream) {
+                                 int T_, const float* extra, const float* extra_gate, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
-    if (y_is_f32) expert_combine_kernel<float><<<T_, 256, 0, stream>>>((const float*)y, place, wts, top, H, c, out);
-    else expert_combine_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)y, place, wts, top, H, c, out);
+    if (y_is_f32) expert_combine_kernel<float><<<T_, 256, 0, stream>>>((const float*)y, place, wts, top, H, c, out, extra, extra_gate);
+    else expert_combine_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)y, place, wts, top, H, c, out, extra, extra_gate);
+    return msgl_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------
+// Clamped gated activation of a packed [gate | up] row:  g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(1.702 g) * (u + 1), in float32, one thread per output element
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ gu, long long stride, int F, float limit,
+                                                          T* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / F;
+    const int c = (int)(i - t * F);
+    const T* row = gu + t * stride;
+    out[i] = from_f32<T>(clamped_gluf_(to_f32<T>(row[c]), to_f32<T>(row[F + c]), limit));
+}
+
+MSGL_API int msgl_clamped_glu(const void* gu, long long stride, int F, float limit, void* out, int T_, int dtype, cudaStream_t stream) {
+    if (T_ <= 0) return MSGL_OK;
+    if (F <= 0 || !(limit > 0.f)) return MSGL_ERR_SIZE;
+    const long long n = (long long)T_ * F;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == MSGL_F32) clamped_glu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, stride, F, limit, (float*)out, n);
+    else if (dtype == MSGL_BF16) clamped_glu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, stride, F, limit, (__nv_bfloat16*)out, n);
+    else return MSGL_ERR_DTYPE;
     return msgl_check_launch();
 }

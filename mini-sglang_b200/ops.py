@@ -1077,12 +1077,15 @@ def _gated_lib():
         lib.msgl_gate_group_norm.argtypes = [c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_ll, c_void_p, c_ll, c_float, c_int,
                                              c_int, c_void_p]
         lib.msgl_unary_act.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int, c_void_p]
-        lib.msgl_route.argtypes = [c_void_p, c_ll, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_route.argtypes = [c_void_p, c_ll, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                   c_void_p, c_void_p]
         lib.msgl_experts_few.argtypes = [c_void_p, c_ll] + [c_void_p] * 4 + [c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
-                                                                            c_void_p]
+                                                                            c_float, c_void_p, c_void_p, c_void_p]
+        lib.msgl_clamped_glu.argtypes = [c_void_p, c_ll, c_int, c_float, c_void_p, c_int, c_int, c_void_p]
         lib.msgl_expert_order.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
         lib.msgl_expert_gather.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p]
-        lib.msgl_expert_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p]
+        lib.msgl_expert_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                                            c_void_p]
         _gated = lib
     return _gated
 
@@ -1329,12 +1332,15 @@ def unary_act(x: torch.Tensor, act: int, scale: float = 1.0, out: Optional[torch
 
 
 def route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], *, n_groups: int, keep: int,
-          top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+          top: int, softmax: bool = False, gate_row: Optional[torch.Tensor] = None):
     """The experts a token uses and their weights.  Scores s = sigmoid(router h) with float32 sums; the choice goes by s +
     correction among the experts of the `keep` best of `n_groups` equal groups of neighbouring experts (a group counts by the sum
     of its two largest choice scores), the `top` largest win; the weights are the winners' s over their sum.
-    h [T, H], router [E, H] -> (int32 [T, top], float32 [T, top])."""
-    _need_cuda(h, router, correction)
+    h [T, H], router [E, H] -> (int32 [T, top], float32 [T, top]).
+    softmax: the logits router h themselves are what the choice goes by (the largest win, the lower index at a tie), and the
+    weights are the softmax over the chosen logits only.  gate_row [H]: one more row that is no expert; the call then returns
+    a third tensor, float32 [T] = sigmoid(gate_row . h)."""
+    _need_cuda(h, router, correction, gate_row)
     T, H = h.shape
     E = router.shape[0]
     assert router.shape == (E, H) and router.is_contiguous() and router.dtype == h.dtype
@@ -1342,18 +1348,30 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tens
         assert correction.dtype == torch.float32 and correction.numel() == E
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    gate_out = None
+    if gate_row is not None:
+        assert gate_row.dtype == h.dtype and gate_row.numel() == H and gate_row.is_contiguous()
+        gate_out = torch.empty(T, dtype=torch.float32, device=h.device)
     code = _gated_lib().msgl_route(_ptr(h), _rows_view(h, H, "h"), _ptr(router), _ptr(correction), H, E, int(n_groups), int(keep),
-                                   int(top), _ptr(idx), _ptr(wts), T, _dt(h), _stream())
+                                   int(top), _ptr(idx), _ptr(wts), T, _dt(h), int(bool(softmax)), _ptr(gate_row), _ptr(gate_out), _stream())
     _check(code, f"route ({E} experts)")
+    if softmax or gate_row is not None:
+        return idx, wts, gate_out
     return idx, wts
 
 
 def experts_few(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
-                scale: float = 1.0) -> torch.Tensor:
+                scale: float = 1.0, limit: float = 0.0, extra: Optional[torch.Tensor] = None,
+                extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """-> float32 [T, H] = scale * sum_k wts[t, k] * down[e] (silu(gate[e] h_t) * (up[e] h_t)), e = idx[t, k], with the chosen
     experts' rows read straight from the stacked weights gate_up [E, 2, F, H] (an expert's gate, then its up) and down [E, H, F]:
-    for a few tokens."""
-    _need_cuda(h, gate_up, down, idx, wts)
+    for a few tokens.  limit > 0: the activation is g * sigmoid(1.702 g) * (u + 1) with g = min(gate, limit) and
+    u = clamp(up, -limit, limit).  extra float32 [T, H] (a shared expert's output) is added inside the sum, times
+    extra_gate float32 [T] where given."""
+    _need_cuda(h, gate_up, down, idx, wts, extra, extra_gate)
+    if extra is not None:
+        assert extra.dtype == torch.float32 and extra.is_contiguous() and tuple(extra.shape) == tuple(h.shape)
+        assert extra_gate is None or (extra_gate.dtype == torch.float32 and extra_gate.numel() == h.shape[0])
     T, H = h.shape
     E, _, F, _ = gate_up.shape
     top = idx.shape[1]
@@ -1363,7 +1381,8 @@ def experts_few(h: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, idx:
     act = torch.empty((T * top, F), dtype=h.dtype, device=h.device)
     out = torch.empty((T, H), dtype=torch.float32, device=h.device)
     code = _gated_lib().msgl_experts_few(_ptr(h), _rows_view(h, H, "h"), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(wts), top, H, F,
-                                         _ptr(act), float(scale), _ptr(out), T, _dt(h), _stream())
+                                         _ptr(act), float(scale), _ptr(out), T, _dt(h), float(limit), _ptr(extra),
+                                         _ptr(extra_gate) if extra is not None else None, _stream())
     _check(code, "experts_few")
     global LAUNCHES
     LAUNCHES += 1
@@ -1393,16 +1412,207 @@ def expert_gather(h: torch.Tensor, place: torch.Tensor, top: int) -> torch.Tenso
     return rows
 
 
-def expert_combine(y: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """-> float32 [T, H] = scale * sum_k wts[t, k] * y[place[t * top + k]]; y [T * top, H] float32 or bfloat16."""
-    _need_cuda(y, place, wts)
+def clamped_glu(gate_up: torch.Tensor, limit: float) -> torch.Tensor:
+    """[T, 2F] (gate first) -> [T, F] = g * sigmoid(1.702 g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    _need_cuda(gate_up)
+    T, F = gate_up.shape[0], gate_up.shape[1] // 2
+    assert gate_up.dim() == 2 and gate_up.shape[1] == 2 * F
+    out = torch.empty((T, F), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_gated_lib().msgl_clamped_glu(_ptr(gate_up), _rows_view(gate_up, 2 * F, "gate_up"), F, float(limit), _ptr(out), T, _dt(gate_up),
+                                         _stream()), "clamped_glu")
+    return out
+
+
+def expert_combine(y: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, scale: float = 1.0, extra: Optional[torch.Tensor] = None,
+                   extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """-> float32 [T, H] = scale * (sum_k wts[t, k] * y[place[t * top + k]] + extra_gate[t] * extra[t]); y [T * top, H] float32 or
+    bfloat16; extra float32 [T, H] and extra_gate float32 [T] are optional (no gate: the extra term counts fully)."""
+    _need_cuda(y, place, wts, extra, extra_gate)
+    if extra is not None:
+        assert extra.dtype == torch.float32 and extra.is_contiguous() and extra.shape[1] == y.shape[1]
+        assert extra_gate is None or (extra_gate.dtype == torch.float32 and extra_gate.numel() == wts.shape[0])
     T, top = wts.shape
     H = y.shape[1]
     assert y.is_contiguous() and y.shape[0] == T * top and wts.dtype == torch.float32 and wts.is_contiguous()
     _dt(y)
     out = torch.empty((T, H), dtype=torch.float32, device=y.device)
     _check(_gated_lib().msgl_expert_combine(_ptr(y), int(y.dtype == torch.float32), _ptr(place), _ptr(wts), top, H, float(scale), _ptr(out),
-                                            T, _stream()), "expert_combine")
+                                            T, _ptr(extra), _ptr(extra_gate) if extra is not None else None, _stream()), "expert_combine")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# attention with a sink, the gated delta rule, scaled sums and the per-layer token input (csrc/mixers_delta.cu)
+# ---------------------------------------------------------------------------------------
+_delta = None
+SINK_ATTENTION_ROWS = 8             # (token, head) rows of a block of the attention kernel with a sink
+SINK_ATTENTION_MAX_HEAD_DIM = 512
+SINK_ATTENTION_SPLIT_KEYS = 256     # keys of a piece when a one-token step cuts a request's keys over several blocks
+DELTA_RULE_MAX_KEY_DIM = 512
+
+
+def _delta_lib():
+    global _delta
+    if _delta is None:
+        lib = _build.delta_mixers_library()
+        lib.msgl_scaled_add_norm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.msgl_rotary_angles.argtypes = [c_void_p, c_void_p, ctypes.c_double, c_void_p, c_int, c_int, c_void_p]
+        lib.msgl_sink_qkv_prep.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_float] + [c_void_p] * 4 + [c_int] * 7 + [c_void_p]
+        lib.msgl_sink_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p] + \
+            [c_int] * 12 + [c_float, c_float, c_int, c_void_p]
+        lib.msgl_delta_rule.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int] + [c_void_p] * 6 + [c_int] * 6 + [c_void_p]
+        lib.msgl_side_gate_mul.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+        _delta = lib
+    return _delta
+
+
+def scaled_add_norm(x: torch.Tensor, scale: torch.Tensor, residual: torch.Tensor, *, weight: Optional[torch.Tensor] = None,
+                    eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """residual += x * scale in float32, in place (scale: float32 [H], one factor per column).  With `weight` (float32 [H])
+    -> rmsnorm(residual) * weight in `out_dtype`, from the same pass; without it -> residual itself in `out_dtype`, or nothing
+    when `out_dtype` is None.  x [T, H] float32 or bfloat16."""
+    _need_cuda(x, scale, residual, weight)
+    T, H = x.shape
+    assert x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16)
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape == x.shape
+    assert scale.dtype == torch.float32 and scale.numel() == H and (weight is None or (weight.dtype == torch.float32 and weight.numel() == H))
+    y = torch.empty((T, H), dtype=out_dtype, device=x.device) if out_dtype is not None else None
+    assert weight is None or y is not None
+    code = _delta_lib().msgl_scaled_add_norm(_ptr(x), int(x.dtype == torch.float32), _ptr(scale), _ptr(residual), _ptr(weight), float(eps),
+                                             _ptr(y), _DT[out_dtype] if out_dtype is not None else 0, T, H, _stream())
+    _check(code, "scaled_add_norm")
+    return y
+
+
+def rotary_angles(positions: torch.Tensor, freq: torch.Tensor, magnitude: float, T: int) -> torch.Tensor:
+    """positions int32 [>= T], freq float64 [n] -> float32 [T, 2n] = magnitude * (cos | sin)(position * freq), the product and the
+    circular functions in double precision."""
+    _need_cuda(positions, freq)
+    assert positions.dtype == torch.int32 and positions.numel() >= T and freq.dtype == torch.float64 and freq.is_contiguous()
+    n = freq.numel()
+    out = torch.empty((T, 2 * n), dtype=torch.float32, device=freq.device)
+    _check(_delta_lib().msgl_rotary_angles(_ptr(positions), _ptr(freq), float(magnitude), _ptr(out), T, n, _stream()), "rotary_angles")
+    return out
+
+
+def sink_qkv_prep(proj: torch.Tensor, *, n_q: int, n_kv: int, d: int, dv: int, angles: Optional[torch.Tensor],
+                  v_first: Optional[torch.Tensor], lam: float, out_loc: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                  v_cache: Optional[torch.Tensor], page_size: int) -> torch.Tensor:
+    """proj [T, >= n_q * d + n_kv * d + n_kv * dv] packed rows [q | k | v | ...].  The first angles.shape[1] elements of every q and
+    k head turn in halves (element i against i + rot / 2) by `angles` float32 [T, rot] = cos | sin of the tokens' positions; v
+    becomes (1 - lam) v + lam v_first where `v_first` [T, n_kv * dv] (a view into packed rows) is given; k goes to `k_cache`
+    [pages, n_kv, page, d] and v to `v_cache` [pages, n_kv, page, dv] at token slots `out_loc`; the q rows come back as [T, n_q, d]."""
+    _need_cuda(proj, angles, v_first, out_loc, k_cache, v_cache)
+    T = proj.shape[0]
+    width = (n_q + n_kv) * d + n_kv * dv
+    stride = _rows_view(proj, proj.shape[1], "proj")
+    assert proj.shape[1] >= width
+    rot = 0
+    if angles is not None:
+        rot = angles.shape[1]
+        assert angles.dtype == torch.float32 and angles.is_contiguous() and angles.shape[0] >= T
+    vf_stride = 0
+    if v_first is not None:
+        assert v_first.dtype == proj.dtype and v_first.shape == (T, n_kv * dv)
+        vf_stride = _rows_view(v_first, n_kv * dv, "v_first")
+    if k_cache is not None:
+        assert k_cache.dtype == proj.dtype and v_cache.dtype == proj.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (n_kv, page_size, d) and tuple(v_cache.shape[1:]) == (n_kv, page_size, dv)
+        assert out_loc is not None and out_loc.dtype == torch.int32 and out_loc.numel() >= T
+    q_out = torch.empty((T, n_q, d), dtype=proj.dtype, device=proj.device)
+    code = _delta_lib().msgl_sink_qkv_prep(_ptr(proj), stride, _ptr(angles), rot, _ptr(v_first), vf_stride, float(lam), _ptr(out_loc),
+                                           _ptr(q_out), _ptr(k_cache), _ptr(v_cache), page_size, n_q, n_kv, d, dv, T, _dt(proj), _stream())
+    _check(code, "sink_qkv_prep")
+    return q_out
+
+
+def sink_attention_geometry(n_q: int, n_kv: int) -> Tuple[int, int]:
+    """(tokens per query tile, query heads of one kv head per block) of the attention kernel with a sink."""
+    gh = min(n_q // n_kv, SINK_ATTENTION_ROWS)
+    return SINK_ATTENTION_ROWS // gh, gh
+
+
+def sink_attention_splits(table_width: int, page_size: int, window: int) -> int:
+    """Pieces a one-token step cuts a request's keys into: as many as the block table's width asks for, or as a window touches."""
+    splits = max(1, -(-(table_width * page_size) // SINK_ATTENTION_SPLIT_KEYS))
+    if window > 0:
+        splits = min(splits, (window - 1) // SINK_ATTENTION_SPLIT_KEYS + 2)
+    return splits
+
+
+def sink_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, q_start: torch.Tensor,
+                   kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int, scale: float, softcap: float,
+                   window: int, sink: torch.Tensor, q_lens: Optional[Sequence[int]], workspace=None) -> None:
+    """Causal softmax attention over the paged cache: the query at position i sees the keys j <= i with i - j < window (window 0:
+    all), score = q . k * scale, capped as softcap * tanh(score / softcap) where softcap > 0, and every softmax's denominator
+    holds exp(sink[head]) besides the seen keys' terms.  q [T, heads, d]; K cache [pages, n_kv, page, d], V cache [pages, n_kv,
+    page, dv]; sink float32 [heads]; out [T, heads * dv].  q_lens: the requests' numbers of tokens as the host knows them (they
+    size the launch), or None when every request brings one token: the keys are then cut into pieces of
+    SINK_ATTENTION_SPLIT_KEYS for blocks of their own, joined in order by a second kernel (workspace: a parts.Workspace for
+    the pieces)."""
+    _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, sink)
+    T, n_q, d = q.shape
+    dv = v_cache.shape[3]
+    assert q.is_contiguous() and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
+    assert sink.dtype == torch.float32 and sink.numel() == n_q
+    out_stride = _rows_view(out, n_q * dv, "out")
+    B = kv_len.numel()
+    QT, GH = sink_attention_geometry(n_q, n_kv)
+    uniform = q_lens is None
+    n_tiles = B if uniform else sum(-(-n // QT) for n in q_lens)
+    splits, part_o, part_ml = 1, None, None
+    if uniform:
+        splits = sink_attention_splits(block_table.shape[1], page_size, int(window))
+        if splits > 1:
+            rows = splits * T * n_q
+            if workspace is not None:
+                part_o, part_ml = workspace.get("sink_attention_o", rows * dv, torch.float32), workspace.get("sink_attention_ml", rows * 2, torch.float32)
+            else:
+                part_o = torch.empty(rows * dv, dtype=torch.float32, device=q.device)
+                part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
+    code = _delta_lib().msgl_sink_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+        n_tiles, _ptr(sink), _ptr(out), out_stride, _ptr(part_o), _ptr(part_ml), splits, SINK_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv, d, dv,
+        page_size, QT, GH, int(window), float(scale), float(softcap), _dt(q), _stream())
+    _check(code, f"sink_attention (head sizes {d}, {dv})")
+    if splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1
+
+
+def delta_rule(qkv: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+               q_lens: Optional[Sequence[int]] = None, workspace=None) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, continued from and written back to `state` [slots, heads, key_dim, value_dim]
+    float32.  qkv [T, 2 * kv_heads * key_dim + heads * value_dim] contiguous (q | k | v as the convolution left them); a, b
+    [T, heads]: views into one packed projection (decay and write-strength pre-activations).  Per head: unit-length q (times
+    key_dim^-1/2) and k, beta = sigmoid(b), g = exp(-exp(a_log) softplus(a + dt_bias)), S <- g S, u = beta (v - S^T k),
+    S <- S + k u^T, o = S^T q.  -> float32 [T, heads * value_dim]."""
+    _need_cuda(qkv, a, b, a_log, dt_bias, state, q_start, slots)
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == 2 * kv_heads * key_dim + heads * value_dim
+    assert a.dtype == qkv.dtype and b.dtype == qkv.dtype and a.shape == (T, heads) and b.shape == (T, heads)
+    stride = _rows_view(a, heads, "a")
+    assert _rows_view(b, heads, "b") == stride
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, key_dim, value_dim)
+    assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == heads and dt_bias.numel() == heads
+    out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=qkv.device)
+    B = q_start.numel() - 1
+    code = _delta_lib().msgl_delta_rule(_ptr(qkv), _ptr(a), stride, 0, _col_off(b, a), _ptr(a_log), _ptr(dt_bias), _ptr(state), _ptr(q_start),
+                                        _ptr(slots), _ptr(out), heads, kv_heads, key_dim, value_dim, B, _dt(qkv), _stream())
+    _check(code, f"delta_rule (key size {key_dim})")
+    return out
+
+
+def side_gate_mul(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, offset: int) -> torch.Tensor:
+    """gate [T, dim], table [V, columns], ids int32 [T] -> [T, dim] = gelu_tanh(gate) * table[ids][offset : offset + dim]."""
+    _need_cuda(gate, table, ids)
+    T, dim = gate.shape
+    assert table.dtype == gate.dtype and table.is_contiguous() and ids.dtype == torch.int32 and ids.numel() >= T
+    out = torch.empty((T, dim), dtype=gate.dtype, device=gate.device)
+    code = _delta_lib().msgl_side_gate_mul(_ptr(gate), _rows_view(gate, dim, "gate"), _ptr(table), table.shape[1], int(offset), _ptr(ids),
+                                           table.shape[0], _ptr(out), dim, T, _dt(gate), _stream())
+    _check(code, "side_gate_mul")
     return out
 
 

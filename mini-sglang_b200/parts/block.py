@@ -6,7 +6,8 @@ from ..weights.loader import TensorDecl
 import torch
 
 from .. import ops
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildEnv, Projected, build_part,
+from ..config.spec import PartSpec
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildEnv, Part, Projected, build_part,
                    register_block)
 
 
@@ -196,4 +197,109 @@ class SandwichResidualBlock(Block):
                                   next_weight=self._w["ffn_in"], next_eps=self.norm_ffn_in.eps, out_dtype=self.env.dtype)
         f = self.ffn.forward(y, ctx)
         ops.postnorm_residual(f, self._w["ffn_out"], self.norm_ffn_out.eps, self.scale, residual, out_dtype=self.env.dtype)
+        return None, residual
+
+
+class TokenSideTable(Part):
+    """A table with one row per token of the vocabulary whose columns are shared out among the layers (layer i reads its own
+    slice of a token's row).  One object holds it for all layers.  params: table (tensor name), vocab_size, columns."""
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.tensor_name, self.V, self.C = spec["table"], int(spec["vocab_size"]), int(spec["columns"])
+        self.table = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.tensor_name: TensorDecl((self.V, self.C))}
+
+    def load(self, src) -> None:
+        if self.table is None:
+            self.table = src.fetch(self.tensor_name).contiguous()
+
+
+@register_block("scaled_side_residual")
+class ScaledSideResidualBlock(Block):
+    """Pre-norm sublayers whose outputs are scaled element by element before they join the float32 stream, and a per-layer
+    token input after them:
+
+        res += m * s1 * mixer(norm_in(res));   res += m * s2 * ffn(norm_post(res))
+        y = Wp (gelu_tanh(Wg res) * E[token][offset : offset + dim]);   res += m * rms(y) * wn
+
+    with one factor m (`residual_scale`) and learned vectors s1, s2 of the width (`mixer_scale_name`, `ffn_scale_name`; full
+    tensor names).  The layer may have no feed-forward.  `side` (or None) describes the token input: E is a table of
+    `columns` columns per token shared by all layers (`table`), this layer reads `dim` of them from `offset`; Wg [dim, H],
+    Wp [H, dim] and the plain RMS-norm weight wn are the layer's own (`gate`, `proj`, `norm`).  The sums, the products
+    m * s and both norms are float32; a scaled sum and the norm that follows it are one kernel, and so are the side input's
+    norm and its sum.  The block hands the stream on with nothing left un-added.  Roles of the norms: "input", "post_mixer"
+    (`rmsnorm`).  block_params: residual_scale, mixer_scale_name, ffn_scale_name, hidden_size, norm_eps, side."""
+
+    def __init__(self, layer_spec, env: BuildEnv):
+        super().__init__(None, layer_spec.prefix, env)
+        at = layer_spec.part_prefix
+        bp = layer_spec.block_params
+        self.m, self.H, self.eps = float(bp.get("residual_scale", 1.0)), int(bp["hidden_size"]), float(bp["norm_eps"])
+        self.position = None
+        if layer_spec.position is not None:
+            self.position = env.shared(layer_spec.position, lambda: build_part(
+                POSITION_ENCODINGS, "position encoding", layer_spec.position, layer_spec.prefix, env))
+        self.norm_in = build_part(NORMS, "norm", layer_spec.norms["input"], at("input"), env)
+        self.mixer = build_part(MIXERS, "mixer", layer_spec.mixer, at("mixer"), env, position=self.position)
+        self.norm_post = self.ffn = None
+        if layer_spec.feed_forward is not None:
+            self.norm_post = build_part(NORMS, "norm", layer_spec.norms["post_mixer"], at("post_mixer"), env)
+            self.ffn = build_part(FEED_FORWARDS, "feed-forward", layer_spec.feed_forward, at("feed_forward"), env)
+            if not hasattr(self.norm_post, "eps"):
+                raise ValueError("this block fuses an RMS norm behind the mixer's sum; another kind of norm is not taken here")
+        self.n_s1, self.n_s2 = bp["mixer_scale_name"], bp.get("ffn_scale_name")
+        self.side = dict(bp["side"]) if bp.get("side") else None
+        self.side_table = None
+        if self.side is not None:
+            tspec = PartSpec("token_side_table", {k: self.side[k] for k in ("table", "vocab_size", "columns")})
+            self.side_table = env.shared(tspec, lambda: TokenSideTable(tspec, "", env))
+        self.s1 = self.s2 = self.w_post = self.side_gate = self.side_proj = self.side_norm = None
+
+    def parts(self):
+        return [p for p in (self.position, self.norm_in, self.mixer, self.norm_post, self.ffn, self.side_table) if p is not None]
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        out: Dict[str, TensorDecl] = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        out[self.n_s1] = TensorDecl((self.H,), kind="vector", init="norm")
+        if self.ffn is not None:
+            out[self.n_s2] = TensorDecl((self.H,), kind="vector", init="norm")
+        if self.side is not None:
+            d = int(self.side["dim"])
+            out[self.side["gate"]] = TensorDecl((d, self.H))
+            out[self.side["proj"]] = TensorDecl((self.H, d))
+            out[self.side["norm"]] = TensorDecl((self.H,), kind="vector", init="norm")
+        return out
+
+    def load(self, src) -> None:
+        for part in self.parts():
+            part.load(src)
+        # m * s in float32: the factor of what a sublayer adds to the stream
+        self.s1 = (src.fetch(self.n_s1).float() * self.m).contiguous()
+        if self.ffn is not None:
+            self.s2 = (src.fetch(self.n_s2).float() * self.m).contiguous()
+            self.w_post = self.norm_post.weight.float().contiguous()
+        if self.side is not None:
+            self.side_gate, self.side_proj = src.fetch(self.side["gate"]).contiguous(), src.fetch(self.side["proj"]).contiguous()
+            self.side_norm = src.fetch(self.side["norm"]).float().contiguous()
+
+    def forward(self, delta, residual, ctx, cache, writes_cache: bool = True):
+        y = self.norm_in.forward(x=delta, residual=residual, residual_out=residual if delta is not None else None)
+        a = self.mixer.forward(y, ctx, cache, writes_cache)
+        dt = self.env.dtype
+        if self.ffn is not None:
+            y = ops.scaled_add_norm(a, self.s1, residual, weight=self.w_post, eps=self.norm_post.eps, out_dtype=dt)
+            f = self.ffn.forward(y, ctx)
+            x = ops.scaled_add_norm(f, self.s2, residual, out_dtype=dt if self.side is not None else None)
+        else:
+            x = ops.scaled_add_norm(a, self.s1, residual, out_dtype=dt if self.side is not None else None)
+        if self.side is not None:
+            gate = ops.linear(x, self.side_gate)
+            g = ops.side_gate_mul(gate, self.side_table.table, ctx.input_ids, int(self.side["offset"]))
+            yv = ops.linear(g, self.side_proj, out_dtype=torch.float32)
+            ops.postnorm_residual(yv, self.side_norm, self.eps, self.m, residual, out_dtype=dt)
         return None, residual

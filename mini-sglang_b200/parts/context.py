@@ -9,7 +9,7 @@ step's tokens are written, so its first new token sits at position kv_len[r] - q
 from __future__ import annotations
 
 import dataclasses
-from typing import Sequence, Dict, List, Optional, Tuple
+from typing import Any, Sequence, Dict, List, Optional, Tuple
 
 import torch
 
@@ -45,6 +45,10 @@ class StepContext:
     uniform_decode: bool = False       # every request brings exactly one token (fixed launch shapes)
     all_rows_wanted: bool = False      # the wanted rows are all T rows in order (what a decode step asks for)
     workspace: Optional["Workspace"] = None
+    # what parts of one forward pass hand to each other within the step (the first layer's values that later layers blend
+    # with their own, the cos | sin rows of the step's positions that layers with the same encoding share); empty at the
+    # start of every step
+    shared: Dict[Any, Any] = dataclasses.field(default_factory=dict)
 
 
 class Workspace:

@@ -90,3 +90,92 @@ class RoutedExperts(FeedForward):
                 y[at:at + n] = ops.linear(a, self.down[e], out_dtype=torch.float32)
                 at += n
         return ops.expert_combine(y, place, wts, self.out_scale)
+
+
+@register_feed_forward("softmax_experts")
+class SoftmaxExperts(FeedForward):
+    """A mixture of small clamped gated feed-forwards chosen by the largest router logits, beside a shared one.
+
+    Router: z = Wr x with float32 sums; the `top` experts with the largest logits are chosen (the lower index wins a tie) and
+    their weights are the softmax over the chosen logits only.  Expert, no biases: g = min(gate_e x, limit),
+    u = clamp(up_e x, -limit, limit), down_e (g * sigmoid(1.702 g) * (u + 1)).  The output is the weighted sum of the chosen
+    experts' outputs in float32.  With `shared_size` > 0 a shared expert of the same form (sizes and limit of its own) runs
+    for every token and is added, times sigmoid(wsg . x), one number per token that the router kernel makes beside its logits.
+
+    The launches are those of `routed_experts`: a few (token, choice) pairs and every CUDA-graph step stream the chosen
+    experts' rows; many tokens are put in the order of their experts for one grouped product each way.
+
+    params: hidden_size, intermediate_size, limit, num_experts, top, shared_size, shared_limit,
+            names (router, expert (with {e}), gate, up, down, shared, shared_gate).
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        s = spec
+        self.H, self.F, self.n_exp, self.top = int(s["hidden_size"]), int(s["intermediate_size"]), int(s["num_experts"]), int(s["top"])
+        self.limit = float(s["limit"])
+        self.Fs, self.shared_limit = int(s.get("shared_size") or 0), float(s.get("shared_limit") or 0.0)
+        if self.n_exp > ops.ROUTE_MAX_EXPERTS:
+            raise ValueError(f"the router kernel takes up to {ops.ROUTE_MAX_EXPERTS} experts")
+        if not 1 <= self.top <= self.n_exp:
+            raise ValueError(f"top = {self.top}: the model has {self.n_exp} experts")
+        names = {"router": "router", "expert": "e{e}", "gate": "gate", "up": "up", "down": "down", "shared": "shared",
+                 "shared_gate": "shared.sg"}
+        names.update(s.get("names") or {})
+        self.names = names
+        self.router = self.down = self.gate_up = self.sh_gate_up = self.sh_down = self.sh_gate = None
+
+    def _expert(self, e: int, what: str) -> str:
+        return self.name(self.names["expert"].format(e=e) + "." + self.names[what])
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        t = {self.name(self.names["router"]): TensorDecl((self.n_exp, self.H), std=0.5)}
+        for e in range(self.n_exp):
+            t[self._expert(e, "gate")] = TensorDecl((self.F, self.H))
+            t[self._expert(e, "up")] = TensorDecl((self.F, self.H))
+            t[self._expert(e, "down")] = TensorDecl((self.H, self.F))
+        if self.Fs:
+            sh = self.name(self.names["shared"])
+            t[f"{sh}.{self.names['gate']}"] = TensorDecl((self.Fs, self.H))
+            t[f"{sh}.{self.names['up']}"] = TensorDecl((self.Fs, self.H))
+            t[f"{sh}.{self.names['down']}"] = TensorDecl((self.H, self.Fs))
+            t[self.name(self.names["shared_gate"])] = TensorDecl((1, self.H), std=0.5)
+        return t
+
+    def load(self, src) -> None:
+        f = src.fetch
+        self.router = f(self.name(self.names["router"])).contiguous()
+        self.gate_up = torch.stack([torch.stack((f(self._expert(e, "gate")), f(self._expert(e, "up")))) for e in range(self.n_exp)]).contiguous()
+        self.down = torch.stack([f(self._expert(e, "down")) for e in range(self.n_exp)]).contiguous()
+        if self.Fs:
+            sh = self.name(self.names["shared"])
+            self.sh_gate_up = torch.cat((f(f"{sh}.{self.names['gate']}"), f(f"{sh}.{self.names['up']}")), dim=0).contiguous()
+            self.sh_down = f(f"{sh}.{self.names['down']}").contiguous()
+            self.sh_gate = f(self.name(self.names["shared_gate"])).reshape(-1).contiguous()
+
+    def forward(self, x, ctx):
+        idx, wts, sgate = ops.route(x, self.router, None, n_groups=1, keep=1, top=self.top, softmax=True, gate_row=self.sh_gate)
+        shared = None
+        if self.Fs:
+            a = ops.clamped_glu(ops.linear(x, self.sh_gate_up), self.shared_limit)
+            shared = ops.linear(a, self.sh_down, out_dtype=torch.float32)
+        T = x.shape[0]
+        if ctx.uniform_decode or T * self.top <= ops.EXPERTS_FEW_PAIRS:
+            return ops.experts_few(x, self.gate_up, self.down, idx, wts, limit=self.limit, extra=shared, extra_gate=sgate)
+        counts, place = ops.expert_order(idx, self.n_exp)
+        rows = ops.expert_gather(x, place, self.top)
+        if x.dtype == torch.bfloat16 and self.H % 8 == 0 and self.F % 8 == 0 and hasattr(torch, "_grouped_mm"):
+            ends = torch.cumsum(counts, 0, dtype=torch.int32)
+            gu = torch._grouped_mm(rows, self.gate_up.view(self.n_exp, 2 * self.F, self.H).transpose(-2, -1), offs=ends)
+            y = torch._grouped_mm(ops.clamped_glu(gu, self.limit), self.down.transpose(-2, -1), offs=ends)
+            return ops.expert_combine(y, place, wts, extra=shared, extra_gate=sgate)
+        y = torch.empty((T * self.top, self.H), dtype=torch.float32, device=x.device)
+        at = 0
+        for e, n in enumerate(counts.tolist()):          # the one read of device data on the host: the experts' row counts
+            if n:
+                a = ops.clamped_glu(ops.linear(rows[at:at + n], self.gate_up[e].view(2 * self.F, self.H)), self.limit)
+                y[at:at + n] = ops.linear(a, self.down[e], out_dtype=torch.float32)
+                at += n
+        return ops.expert_combine(y, place, wts, extra=shared, extra_gate=sgate)

@@ -76,6 +76,7 @@ class DecoderModel:
         """-> float32 logits [len(want_rows), vocab] (all T rows if want_rows is None)."""
         if self.fused_decode is not None and self.fused_decode.takes(ctx):
             return self.fused_decode.forward(ctx, caches)       # the whole step in one persistent kernel
+        ctx.shared.clear()          # what the parts of one pass hand to each other starts empty (a context may be run again)
         if NVTX_RANGES:
             return self._forward_marked(ctx, caches, want_rows)
         residual = self.embedding.forward(ctx.input_ids, ctx)
