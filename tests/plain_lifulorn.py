@@ -115,7 +115,7 @@ def sink_attention(u, w, p: str, c: dict, kind: str, v_first: Optional[torch.Ten
     mask = c.get("mask")
     if mask:
         seen = seen & (i - j < int(mask["size"]))
-    cap = c.get("softcap")
+    cap = c.get("softcap") if kind == "attention_2" else None        # only the second kind caps its scores
     out = torch.zeros(T, H, dv, dtype=u.dtype)
     for h in range(H):
         g = h // (H // G)
@@ -173,12 +173,16 @@ def clamped_expert(u, w, p: str, limit: float):
     return (g * torch.sigmoid(1.702 * g) * (up + 1.0)) @ w[p + ".down"].T
 
 
-def expert_mixture(u, w, p: str, c: dict):
+def expert_mixture(u, w, p: str, c: dict, margins: Optional[list] = None):
     """Every token's `top` experts by router logit, weighted by the softmax over the chosen logits, plus a shared expert
-    times the sigmoid of one number per token."""
+    times the sigmoid of one number per token.  margins, if given, receives per token the gap between the smallest chosen
+    logit and the largest one that was not chosen (how close the choice was)."""
     r = c["router"]
     z = u @ w[p + ".router"].T
     top, idx = torch.topk(z, int(r["top"]), dim=1)
+    if margins is not None and int(r["top"]) < z.shape[1]:
+        ordered = z.sort(dim=1, descending=True).values
+        margins.append(ordered[:, int(r["top"]) - 1] - ordered[:, int(r["top"])])
     wt = torch.softmax(top, dim=1)
     out = torch.zeros_like(u)
     for e in range(int(r["experts"])):
@@ -201,8 +205,10 @@ def token_side(x, tokens, w, layer: int, side_dim: int, eps: float):
 
 # -- the model ------------------------------------------------------------------------------------------------------
 
-def forward_sequence(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float32, layers_out: Optional[list] = None):
-    """-> logits [T, vocab] for every place of the sequence.  layers_out, if given, receives the stream after every layer."""
+def forward_sequence(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float32, layers_out: Optional[list] = None,
+                     margins: Optional[list] = None):
+    """-> logits [T, vocab] for every place of the sequence.  layers_out, if given, receives the stream after every layer;
+    margins the routers' gaps between the last chosen and the first unchosen logit, one tensor [T] per routed layer."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(cfg["norm"]["eps"])
     m = float(cfg.get("residual_mult", 1.0))
@@ -224,7 +230,7 @@ def forward_sequence(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], d
         x = x + m * a * w[p + ".ls1"]
         if layer.get("mlp") is not None:
             u = rms_norm(x, w[p + ".norm2"], eps)
-            x = x + m * expert_mixture(u, w, p + ".mlp", layer["mlp"]) * w[p + ".ls2"]
+            x = x + m * expert_mixture(u, w, p + ".mlp", layer["mlp"], margins) * w[p + ".ls2"]
         if side:
             x = x + m * token_side(x, tokens, w, i, int(side["dim"]), eps)
         if layers_out is not None:
