@@ -594,6 +594,34 @@ def pepevik_config(size, layers, vocab):
             "embedding": {"scale": float(s["width"]) ** 0.5}, "max_positions": 8192, "layers": [kinds[i % 4] for i in range(layers)]}
 
 
+def lifulorn_config(size, layers, vocab, window=1024):
+    """A Lifulorn model with the given layer sizes.  The attentions have the heads of the Qwen3 layer (key and value size of the
+    head), half of every head rotated with scaled frequencies, a window, blended values; the delta-rule mixer has as many value
+    heads of 128 as fill the width on half as many key heads of 128, four taps; every layer has 32 clamped experts of a quarter
+    of the layer's feed-forward width of which a token uses 4, beside a shared expert of that width, and a token input of 128
+    columns.  Kinds of layers in turn: delta rule, attention, attention, attention of the second kind."""
+    s = COMPARE_SIZES[size]
+    rot = {"base": 50000.0, "dims": s["dim"] // 2}
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+           "mask": {"size": window}, "v_mix": True}
+    a1 = {"type": "attention", "mixer": dict(att, rot=dict(rot, scaling={"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}))}
+    a2 = {"type": "attention_2", "mixer": dict(att, softcap=50.0, rot=dict(rot, scaling={"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}))}
+    heads = s["width"] // 128
+    dl = {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(heads // 2, 1), "dim": 128, "vdim": 128, "conv": 4}}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"] // 4, "limit": 7.0}, "router": {"experts": 32, "top": 4},
+           "shared": {"ff": s["ff"] // 4, "limit": 7.0}}
+    kinds = [dict(dl, mlp=moe), dict(a1, mlp=moe), dict(a1, mlp=moe), dict(a2, mlp=moe)]
+    return {"architecture": "Lifulorn", "width": s["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "token_side": {"dim": 128}, "layers": [kinds[i % 4] for i in range(layers)]}
+
+
+def workload_lifulorn(args):
+    """As --workload vekurax_compare, with a Lifulorn model (`lifulorn_config`) beside the Pepevik model of equal sizes (the
+    engine's other design with routed experts, a recurrence with a short convolution and an attention whose key and value rows
+    have sizes of their own)."""
+    return workload_vekurax(args, name="lifulorn", config=lifulorn_config, beside="pepevik")
+
+
 def workload_pepevik(args):
     """As --workload vekurax_compare, with a Pepevik model (`pepevik_config`) beside the Vekurax model of equal sizes (the engine's
     other design whose mixer is an attention and a recurrence side by side)."""
@@ -631,7 +659,9 @@ def workload_vekurax(args, name="vekurax", config=None, beside="qwen3"):
                     num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=V,
                     tie_word_embeddings=True, max_position_embeddings=CTX + 4096)
         res = {}
-        for arch, cfg in ((name, config(size, L, V)), (beside, qwen if beside == "qwen3" else vekurax_config(size, L, V))):
+        others = {"qwen3": lambda: qwen, "vekurax": lambda: vekurax_config(size, L, V), "pepevik": lambda: pepevik_config(size, L, V)}
+        archs = ((name, config(size, L, V)),) if args.alone else ((name, config(size, L, V)), (beside, others[beside]()))
+        for arch, cfg in archs:
             tmp = tempfile.mkdtemp(prefix="msgl_bench_")
             with open(os.path.join(tmp, "config.json"), "w") as f:
                 json.dump(cfg, f)
@@ -706,9 +736,11 @@ def main():
     ap.add_argument("--profiler-range", action="store_true",
                     help="cudaProfilerStart/Stop around the timed region (ncu --profile-from-start off)")
     ap.add_argument("--no-graph", action="store_true", help="decode without CUDA graphs")
-    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare", "pepevik_compare"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "qwen3_0.6b_mixed", "qwen3_32b_long", "sweep", "vekurax_compare", "nametar_compare", "pepevik_compare",
+                                                              "lifulorn_compare"],
                     help="headline: the default line; the others: further workloads, one JSON line each")
-    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare / pepevik_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
+    ap.add_argument("--sizes", default=None, help="--workload vekurax_compare / nametar_compare / pepevik_compare / lifulorn_compare: layer sizes to run, of " + ",".join(COMPARE_SIZES))
+    ap.add_argument("--alone", action="store_true", help="the compare workloads: run the named design only, not the one beside it")
     ap.add_argument("--skip-sanity", action="store_true", help="no comparison with the plain implementation before timing")
     ap.add_argument("--model", default="8b", choices=["8b", "32b", "0.6b"], help="layer sizes for --only decode / prefill")
     ap.add_argument("--lengths", default=None,
@@ -734,6 +766,8 @@ def main():
         return workload_nametar(args)
     if args.workload == "pepevik_compare":
         return workload_pepevik(args)
+    if args.workload == "lifulorn_compare":
+        return workload_lifulorn(args)
 
     import torch
 

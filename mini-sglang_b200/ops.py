@@ -1460,7 +1460,11 @@ def _delta_lib():
         lib.msgl_sink_qkv_prep.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll, c_float] + [c_void_p] * 4 + [c_int] * 7 + [c_void_p]
         lib.msgl_sink_attention.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p] + \
             [c_int] * 12 + [c_float, c_float, c_int, c_void_p]
-        lib.msgl_delta_rule.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int] + [c_void_p] * 6 + [c_int] * 6 + [c_void_p]
+        lib.msgl_sink_attention_mma.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p] + \
+            [c_int] * 10 + [c_float, c_float, c_void_p]
+        lib.msgl_delta_rule.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int] + [c_void_p] * 7 + [c_int] * 7 + [c_void_p]
+        lib.msgl_delta_rule_scratch.argtypes = [c_int] * 4
+        lib.msgl_delta_rule_scratch.restype = c_ll
         lib.msgl_side_gate_mul.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         _delta = lib
     return _delta
@@ -1526,10 +1530,20 @@ def sink_qkv_prep(proj: torch.Tensor, *, n_q: int, n_kv: int, d: int, dv: int, a
     return q_out
 
 
-def sink_attention_geometry(n_q: int, n_kv: int) -> Tuple[int, int]:
-    """(tokens per query tile, query heads of one kv head per block) of the attention kernel with a sink."""
-    gh = min(n_q // n_kv, SINK_ATTENTION_ROWS)
-    return SINK_ATTENTION_ROWS // gh, gh
+SINK_ATTENTION_MMA_ROWS = 64        # rows of a block of the tensor-core kernel
+SINK_ATTENTION_MMA_MAX_HEAD_DIM = 128
+
+
+def sink_attention_geometry(n_q: int, n_kv: int, tensor_cores: bool = False) -> Tuple[int, int]:
+    """(tokens per query tile, query heads of one kv head per block) of the attention kernels with a sink."""
+    rows = SINK_ATTENTION_MMA_ROWS if tensor_cores else SINK_ATTENTION_ROWS
+    gh = min(n_q // n_kv, rows)
+    return rows // gh, gh
+
+
+def sink_attention_on_tensor_cores(dtype: torch.dtype, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel takes these rows: bfloat16, head sizes in steps of 8 up to 128."""
+    return dtype == torch.bfloat16 and d % 8 == 0 and dv % 8 == 0 and max(d, dv) <= SINK_ATTENTION_MMA_MAX_HEAD_DIM
 
 
 def sink_attention_splits(table_width: int, page_size: int, window: int) -> int:
@@ -1542,14 +1556,16 @@ def sink_attention_splits(table_width: int, page_size: int, window: int) -> int:
 
 def sink_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, q_start: torch.Tensor,
                    kv_len: torch.Tensor, block_table: torch.Tensor, n_kv: int, page_size: int, scale: float, softcap: float,
-                   window: int, sink: torch.Tensor, q_lens: Optional[Sequence[int]], workspace=None) -> None:
+                   window: int, sink: torch.Tensor, q_lens: Optional[Sequence[int]], workspace=None,
+                   tensor_cores: Optional[bool] = None) -> None:
     """Causal softmax attention over the paged cache: the query at position i sees the keys j <= i with i - j < window (window 0:
     all), score = q . k * scale, capped as softcap * tanh(score / softcap) where softcap > 0, and every softmax's denominator
     holds exp(sink[head]) besides the seen keys' terms.  q [T, heads, d]; K cache [pages, n_kv, page, d], V cache [pages, n_kv,
     page, dv]; sink float32 [heads]; out [T, heads * dv].  q_lens: the requests' numbers of tokens as the host knows them (they
     size the launch), or None when every request brings one token: the keys are then cut into pieces of
     SINK_ATTENTION_SPLIT_KEYS for blocks of their own, joined in order by a second kernel (workspace: a parts.Workspace for
-    the pieces)."""
+    the pieces).  tensor_cores: None = the bfloat16 kernel with mma products where it takes the sizes
+    (`sink_attention_on_tensor_cores`), the float32-arithmetic one elsewhere; False = the float32-arithmetic kernel in any case."""
     _need_cuda(q, out, k_cache, v_cache, q_start, kv_len, block_table, sink)
     T, n_q, d = q.shape
     dv = v_cache.shape[3]
@@ -1557,7 +1573,9 @@ def sink_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     assert sink.dtype == torch.float32 and sink.numel() == n_q
     out_stride = _rows_view(out, n_q * dv, "out")
     B = kv_len.numel()
-    QT, GH = sink_attention_geometry(n_q, n_kv)
+    if tensor_cores is None:
+        tensor_cores = sink_attention_on_tensor_cores(q.dtype, d, dv) and out_stride % 2 == 0 and out.data_ptr() % 4 == 0
+    QT, GH = sink_attention_geometry(n_q, n_kv, tensor_cores)
     uniform = q_lens is None
     n_tiles = B if uniform else sum(-(-n // QT) for n in q_lens)
     splits, part_o, part_ml = 1, None, None
@@ -1570,10 +1588,16 @@ def sink_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
             else:
                 part_o = torch.empty(rows * dv, dtype=torch.float32, device=q.device)
                 part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
-    code = _delta_lib().msgl_sink_attention(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
-        n_tiles, _ptr(sink), _ptr(out), out_stride, _ptr(part_o), _ptr(part_ml), splits, SINK_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv, d, dv,
-        page_size, QT, GH, int(window), float(scale), float(softcap), _dt(q), _stream())
+    if tensor_cores:
+        code = _delta_lib().msgl_sink_attention_mma(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+            n_tiles, _ptr(sink), _ptr(out), out_stride, _ptr(part_o), _ptr(part_ml), splits, SINK_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv, d,
+            dv, page_size, int(window), float(scale), float(softcap), _stream())
+    else:
+        code = _delta_lib().msgl_sink_attention(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), int(uniform),
+            n_tiles, _ptr(sink), _ptr(out), out_stride, _ptr(part_o), _ptr(part_ml), splits, SINK_ATTENTION_SPLIT_KEYS, T, B, n_q, n_kv, d,
+            dv, page_size, QT, GH, int(window), float(scale), float(softcap), _dt(q), _stream())
     _check(code, f"sink_attention (head sizes {d}, {dv})")
     if splits > 1:
         global LAUNCHES
@@ -1598,9 +1622,15 @@ def delta_rule(qkv: torch.Tensor, a: torch.Tensor, b: torch.Tensor, *, heads: in
     assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and a_log.numel() == heads and dt_bias.numel() == heads
     out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=qkv.device)
     B = q_start.numel() - 1
+    # what does not depend on the state (unit q and k, beta, g) is made for all tokens at once by a kernel of its own
+    numel = int(_delta_lib().msgl_delta_rule_scratch(T, heads, kv_heads, key_dim))
+    scratch = workspace.get("delta_rule_prep", numel, torch.float32) if workspace is not None else \
+        torch.empty(numel, dtype=torch.float32, device=qkv.device)
     code = _delta_lib().msgl_delta_rule(_ptr(qkv), _ptr(a), stride, 0, _col_off(b, a), _ptr(a_log), _ptr(dt_bias), _ptr(state), _ptr(q_start),
-                                        _ptr(slots), _ptr(out), heads, kv_heads, key_dim, value_dim, B, _dt(qkv), _stream())
+                                        _ptr(slots), _ptr(out), _ptr(scratch), heads, kv_heads, key_dim, value_dim, T, B, _dt(qkv), _stream())
     _check(code, f"delta_rule (key size {key_dim})")
+    global LAUNCHES
+    LAUNCHES += 1
     return out
 
 
