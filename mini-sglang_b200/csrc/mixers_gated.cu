@@ -1883,9 +1883,35 @@ __global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ 
     out[i] = from_f32<T>(clamped_gluf_(to_f32<T>(row[c]), to_f32<T>(row[F + c]), limit));
 }
 
+// the same, 16 bytes of gate and of up a thread
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_vec_kernel(const T* __restrict__ gu, long long stride, int F, float limit,
+                                                              T* __restrict__ out, long long n_vec) {
+    constexpr int V = VecOf<T>::N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int per_row = F / V;
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * V;
+    float g[V], u[V], o[V];
+    VecOf<T>::load(gu + t * stride + c, g);
+    VecOf<T>::load(gu + t * stride + F + c, u);
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = clamped_gluf_(g[k], u[k], limit);
+    VecOf<T>::store(out + t * F + c, o);
+}
+
 MSGL_API int msgl_clamped_glu(const void* gu, long long stride, int F, float limit, void* out, int T_, int dtype, cudaStream_t stream) {
     if (T_ <= 0) return MSGL_OK;
     if (F <= 0 || !(limit > 0.f)) return MSGL_ERR_SIZE;
+    const int V = dtype == MSGL_F32 ? 4 : 8;
+    if ((dtype == MSGL_F32 || dtype == MSGL_BF16) && F % V == 0 && stride % V == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const long long n_vec = (long long)T_ * (F / V);
+        const unsigned vb = (unsigned)((n_vec + 255) / 256);
+        if (dtype == MSGL_F32) clamped_glu_vec_kernel<float><<<vb, 256, 0, stream>>>((const float*)gu, stride, F, limit, (float*)out, n_vec);
+        else clamped_glu_vec_kernel<__nv_bfloat16><<<vb, 256, 0, stream>>>((const __nv_bfloat16*)gu, stride, F, limit, (__nv_bfloat16*)out, n_vec);
+        return msgl_check_launch();
+    }
     const long long n = (long long)T_ * F;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == MSGL_F32) clamped_glu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, stride, F, limit, (float*)out, n);

@@ -236,3 +236,11 @@ def forward_sequence(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], d
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    toks = list(prompt)
+    for _ in range(n):
+        with torch.no_grad():
+            toks.append(int(forward_sequence(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]

@@ -653,14 +653,6 @@ def test_random_configurations(seed):
         r.mgr.check_idle()
 
 
-def _greedy(cfg, w, prompt, n):
-    toks = list(prompt)
-    for _ in range(n):
-        with torch.no_grad():
-            toks.append(int(pl.forward_sequence(cfg, w, toks)[-1].argmax()))
-    return toks[len(prompt):]
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(dtype):
     """Engine.generate with the scheduler: prompts of unequal lengths, portions of at most 16 tokens, a small pool."""
@@ -675,7 +667,7 @@ def test_greedy_generation_through_the_entry_point(dtype):
         got = o["token_ids"]
         assert len(got) == 12
         if dtype == "float32":
-            assert got == _greedy(cfg, weights(name), p, 12)
+            assert got == pl.greedy_generate(cfg, weights(name), p, 12)
         else:
             toks = list(p)
             for t in got:           # bfloat16 may take another of two nearly equal logits, or another expert at a router's close call
