@@ -816,9 +816,15 @@ MSGL_API int msgl_sink_attention_mma(const void* q, const void* k_cache, const v
 // ---------------------------------------------------------------------------------------
 #define DR_WCOLS 4
 #define DR_PARTS 8
+#ifndef DR_TB
 #define DR_TB 16
+#endif
+#ifndef DR_FEW_WARPS
 #define DR_FEW_WARPS 4
+#endif
+#ifndef DR_MANY_WARPS
 #define DR_MANY_WARPS 8
+#endif
 
 struct DeltaParams {
     const void* qkv; const void* proj; long long proj_stride; int a_off, b_off;
